@@ -60,6 +60,34 @@ class KVNeed:
     window: Optional[int] = None      # None: all earlier keys; w: the last w keys
     planes: int = 2                   # 2: keys and values; 1: one row per token that attention reads as both
                                       # (a layer that caches a latent from which keys and values are made)
+    chunk: Optional[int] = None       # C: a query sees the earlier keys of its own run of C positions (runs counted
+                                      # from position 0); excludes a window
+
+    @property
+    def bounded(self) -> bool:
+        """Whether keys far enough back are never read again (their pages can be given back)."""
+        return self.window is not None or self.chunk is not None
+
+    def first_needed(self, length: int) -> int:
+        """Lowest key position that a token at position >= ``length`` can still attend."""
+        if self.window is not None:
+            return max(0, length - self.window + 1)
+        if self.chunk is not None:
+            return length - length % self.chunk
+        return 0
+
+    def merged(self, other: "KVNeed") -> Optional["KVNeed"]:
+        """The need of a cache layer that two runs with different masks read (one of them writes it): the same
+        rows, kept for as long as either run can look back; None if the two do not fit one cache layer."""
+        if (self.n_kv_heads, self.head_dim, self.planes) != (other.n_kv_heads, other.head_dim, other.planes):
+            return None
+        if self == other:
+            return self
+        if not (self.bounded and other.bounded):
+            return KVNeed(self.n_kv_heads, self.head_dim, None, self.planes)
+        # a chunk of C never looks back further than a window of C
+        reach = max(self.window or self.chunk, other.window or other.chunk)
+        return KVNeed(self.n_kv_heads, self.head_dim, reach, self.planes)
 
 
 @dataclass(frozen=True)
@@ -172,9 +200,7 @@ class CacheGroup:
 
     def first_needed_position(self, length: int) -> int:
         """Lowest key position that a token at position >= ``length`` can still attend."""
-        if self.need.window is None:
-            return 0
-        return max(0, length - self.need.window + 1)
+        return self.need.first_needed(length)
 
 
 class CacheManager:
@@ -377,7 +403,7 @@ class CacheManager:
 
     def commit_many(self, requests: Sequence[Hashable]) -> None:
         """``commit`` for several requests at once."""
-        if any(group.need.window is not None for group in self.groups):
+        if any(group.need.bounded for group in self.groups):
             for request in requests:                # pages that a window has passed are released one by one
                 self.commit(request)
             return
@@ -419,7 +445,7 @@ class CacheManager:
         self.pending[slot] = 0
         length = int(self.lengths[slot])
         for group_index, group in enumerate(self.groups):
-            if group.need.window is None:
+            if not group.need.bounded:
                 continue
             first = group.first_needed_position(length)
             table = group.tables[request]

@@ -163,7 +163,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int p = positions[t];
     const int item = token_item[t];
     const int first_new = (q_start && kv_len) ? kv_len[item] - (q_start[item + 1] - q_start[item]) : 0;
-    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int lo = first_visible_key(p, window);
     const int first_chunk = lo >> chunk_log2, last_chunk = p >> chunk_log2;
     const int first_split = first_chunk / split_chunks, last_split = last_chunk / split_chunks;
     const int n_active = last_split - first_split + 1;

@@ -105,7 +105,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int rows = min(BQ, q_len - qb * BQ);                    // valid query rows of the block
     const int tok0 = qs + qb * BQ;
     const int hi = pos0 + step * (rows - 1);                       // last key any row may see
-    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int lo = first_visible_key(pos0, window);
     int kb_first = lo / BKEY, kb_last = hi / BKEY;
     if (partial) {
         // The key tiles of an item shared out over gridDim.z CTAs (rows of one position, few items: one CTA per item
@@ -158,6 +158,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     }
     const int row0 = warp * 16 + gq, row1 = row0 + 8;            // the two query rows of this thread
     const int pos_r0 = pos0 + step * row0, pos_r1 = pos0 + step * row1;
+    const int lo_r0 = first_visible_key(pos_r0, window), lo_r1 = first_visible_key(pos_r1, window);
+    const int lo_all = first_visible_key(hi, window);           // the first key that every row of the block sees
 
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks)
@@ -188,7 +190,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         }
         // ---- scale, mask, online softmax
         const int key0 = kb * BKEY;
-        const bool need_mask = (key0 + BKEY - 1 > pos0) || (window > 0 && key0 < hi - window + 1) || rows < BQ;
+        const bool need_mask = (key0 + BKEY - 1 > pos0) || key0 < lo_all || rows < BQ;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < BKEY / 8; ++nt) {
@@ -199,7 +201,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                     int key = key0 + nt * 8 + tq * 2 + (e & 1);
                     int pos = (e < 2) ? pos_r0 : pos_r1;
                     int row = (e < 2) ? row0 : row1;
-                    bool ok = key <= pos && row < rows && (window <= 0 || key > pos - window);
+                    int first = (e < 2) ? lo_r0 : lo_r1;
+                    bool ok = key <= pos && row < rows && key >= first;
                     if (!ok) v = -INFINITY;
                 }
                 s[nt][e] = v;

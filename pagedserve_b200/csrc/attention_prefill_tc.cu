@@ -228,7 +228,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int rows = min(BQ, q_len - qb * BQ);
     const int tok0 = qs + qb * BQ;
     const int hi = pos0 + rows - 1;
-    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int lo = first_visible_key(pos0, window);
     const int kb_first = lo / BKEY, kb_last = hi / BKEY;
     // the item's block-table row: item_row[item] where the table is kept by request slot, else the item itself
     const int* bt = block_table + (size_t)(item_row ? item_row[item] : item) * bt_stride;
@@ -339,6 +339,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int half = SPLIT == 2 ? (warp - 2) >> 2 : 0;        // which keys of a tile / which output columns
         const int r = quarter * 32 + lane;                        // query row of the tile = TMEM lane
         const int pos = pos0 + r;
+        const int lo_row = first_visible_key(pos, window);        // this row's first visible key
+        const int lo_all = first_visible_key(hi, window);         // the first key that every row of the block sees
         const int col0 = half * COLS;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         constexpr int OCOLS = HD / SPLIT;                         // columns of O that this thread owns
@@ -366,10 +368,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int j = 0; j < COLS; ++j)
                     sr[j] = __float_as_uint(extras.cap_log2 * tanh_ex2(__uint_as_float(sr[j]) * extras.scale_over_cap));
             }
-            const bool need_mask = (key0 + COLS - 1 > pos0) || (window > 0 && key0 < pos0 + rows - window) || rows < BQ;
+            const bool need_mask = (key0 + COLS - 1 > pos0) || key0 < lo_all || rows < BQ;
             if (need_mask) {
                 // keys this row may see: [max(lo_row, lo), pos]; everything else becomes -inf
-                const int first_ok = (r < rows) ? max(lo, window > 0 ? pos - window + 1 : 0) - key0 : COLS;
+                const int first_ok = (r < rows) ? lo_row - key0 : COLS;
                 const int last_ok = (r < rows) ? pos - key0 : -1;
 #pragma unroll
                 for (int j = 0; j < COLS; ++j)

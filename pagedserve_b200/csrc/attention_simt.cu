@@ -124,7 +124,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
         q_s[d] = to_float(q[(size_t)t * q_stride + h * head_dim + d]);
     __syncthreads();
 
-    int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    int lo = first_visible_key(p, window);
     int first_tile = lo >> 5, last_tile = p >> 5;
     constexpr int NACC = ATT_MAX_HD / 32;
     float acc[NACC];

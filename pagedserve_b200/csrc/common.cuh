@@ -87,6 +87,15 @@ __device__ __forceinline__ void apply_act_all(float (&v)[N], int act) {
     }
 }
 
+// Which keys a query at position `pos` sees besides "none later than itself", as the attention kernels take it in
+// their `window` argument: w > 0, the last w keys (a sliding window); w < 0, the keys of its own run of -w positions,
+// runs counted from position 0 of the sequence (a chunked mask); 0, every earlier key.  The first visible key:
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -2,18 +2,25 @@
 //
 // moe_route, one CTA per token, float32 throughout:
 //     z = W_router h                    (E numbers; the operands may be bfloat16, sums are float32)
-//     s = softmax(z) over all E experts
+//     s = softmax(z) over all E experts, or s = sigmoid(z) expert by expert (score_kind 1)
 //     with groups: the experts are `groups` runs of E / groups neighbours; a group's mark is its largest s; only
 //     experts of the `keep` groups with the largest marks stand for election
 //     the `top` largest s among them are chosen (ties: the lower index), and their weights are s / (sum of the
-//     chosen s + 1e-20); the lanes of one warp hold the scores and run every round together
+//     chosen s + 1e-20), or the chosen s themselves (normalize 0); the lanes of one warp hold the scores and run
+//     every round together
 //     shared gate: sigmoid(w_sg . h), one number per token (where the layer has a shared expert)
 // Results: dense weights [T, E] (0 where an expert is not chosen), the chosen experts and their weights
 // [T, top], and the shared gate [T].
 //
+// The inner activation of a gated expert from its gate and up pre-activations g, u and the token's weight w
+// (GateForm):
+//     kind 0:  silu(g) * u * w                                   (the weight scales the expert's output)
+//     kind 1:  g' = min(w g, limit), u' = clamp(w u, -limit, limit);  g' * sigmoid(alpha g') * (u' + 1)
+//              (the weight scales the expert's input: without biases W (w h) = w (W h), so it is applied to the
+//              pre-activations in float32; the shared expert's columns have a limit of their own)
 // moe_gate_mul: inner[t, c] = silu(gate) * up * weight[t, expert of column c] over one stacked product of all
 // experts: expert e's block of 2 F columns is its gate columns, then its up columns; the shared expert's block
-// follows the experts' (weight = the shared gate).  inner's columns [e * F, (e + 1) * F) belong to expert e, those
+// follows the experts' (weight = the shared gate, or 1 without one; E = 0: a dense gated feed-forward).  inner's columns [e * F, (e + 1) * F) belong to expert e, those
 // from E * F on to the shared expert.  Products in float32, rounded once.
 //
 // With many tokens the rows are sorted by expert instead (moe_plan, moe_gather, the products over tiles that
@@ -53,13 +60,27 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
+struct GateForm {
+    int kind;                 // 0: silu(g) u w; 1: clamped, weight on the input (see the top of the file)
+    float limit;              // kind 1: the routed experts' limit
+    float shared_limit;       // kind 1: the shared expert's
+    float alpha;              // kind 1: the sigmoid's slope
+};
+
+__device__ __forceinline__ float gated_inner(float g, float u, float w, int kind, float limit, float alpha) {
+    if (kind == 0) return silu(g) * u * w;
+    g = fminf(g * w, limit);
+    u = fminf(fmaxf(u * w, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32, 8)
 moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int router_stride,
                  const T* __restrict__ shared_gate_w, float* __restrict__ dense, int* __restrict__ chosen,
                  float* __restrict__ chosen_w, float* __restrict__ shared_gate, int tokens, int W, int E, int top,
                  int groups, int keep, int by8, const float* __restrict__ raw, int raw_stride,
-                 const float* __restrict__ gain, float eps, T* __restrict__ x_out) {
+                 const float* __restrict__ gain, float eps, T* __restrict__ x_out, int score_kind, int normalize) {
     pdl_prologue();
     x = pdl_fresh(x);
     raw = pdl_fresh(raw);
@@ -177,15 +198,16 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
-        mine[i] = lane + 32 * i < E ? expf(mine[i] - top_z) : 0.f;
+        if (score_kind == 1) mine[i] = lane + 32 * i < E ? 1.0f / (1.0f + expf(-mine[i])) : 0.f;      // sigmoid
+        else mine[i] = lane + 32 * i < E ? expf(mine[i] - top_z) : 0.f;
         sum += mine[i];
     }
     sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
+    const float inv = score_kind == 1 ? 1.0f : 1.0f / sum;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
         const int e = lane + 32 * i;
-        mine[i] = e < E ? mine[i] * inv : -INFINITY;           // the softmax; -inf: no such expert
+        mine[i] = e < E ? mine[i] * inv : -INFINITY;           // the scores; -inf: no such expert
         if (e < E) {
             score[e] = mine[i];
             dense[(size_t)t * E + e] = 0.f;
@@ -258,7 +280,7 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
         if (best_e >= 0) total += best;
     }
     __syncwarp();
-    const float scale = 1.0f / (total + 1e-20f);
+    const float scale = normalize ? 1.0f / (total + 1e-20f) : 1.0f;
     for (int k = lane; k < top; k += 32) {
         const int e = winner[k];
         const float w = winner_score[k] * scale;
@@ -272,7 +294,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_gate_mul_kernel(const T* __restrict__ gate_up, int gu_stride, const float* __restrict__ dense,
                     const float* __restrict__ shared_gate, T* __restrict__ inner, int inner_stride, int tokens,
-                    int columns, int E, int F, int by8) {
+                    int columns, int E, int F, int by8, GateForm form) {
     pdl_prologue();
     gate_up = pdl_fresh(gate_up);
     dense = pdl_fresh(dense);
@@ -285,7 +307,8 @@ moe_gate_mul_kernel(const T* __restrict__ gate_up, int gu_stride, const float* _
              i += (long long)gridDim.x * blockDim.x) {
             const int t = (int)(i / groups), c = (int)(i - (long long)t * groups) << 3;
             const int e = c < E * F ? c / F : E;
-            const float w = e < E ? dense[(size_t)t * E + e] : shared_gate[t];
+            const float w = e < E ? dense[(size_t)t * E + e] : (shared_gate ? shared_gate[t] : 1.0f);
+            const float limit = e < E ? form.limit : form.shared_limit;
             float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (w != 0.f) {
                 const int j = c - e * F;
@@ -294,7 +317,7 @@ moe_gate_mul_kernel(const T* __restrict__ gate_up, int gu_stride, const float* _
                 load8(block + j, g);
                 load8(block + (e < E ? F : shared_ff) + j, u);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = silu(g[k]) * u[k] * w;
+                for (int k = 0; k < 8; ++k) v[k] = gated_inner(g[k], u[k], w, form.kind, limit, form.alpha);
             }
             store8(inner + (size_t)t * inner_stride + c, v);
         }
@@ -304,13 +327,14 @@ moe_gate_mul_kernel(const T* __restrict__ gate_up, int gu_stride, const float* _
          i += (long long)gridDim.x * blockDim.x) {
         const int t = (int)(i / columns), c = (int)(i - (long long)t * columns);
         const int e = c < E * F ? c / F : E;
-        const float w = e < E ? dense[(size_t)t * E + e] : shared_gate[t];
+        const float w = e < E ? dense[(size_t)t * E + e] : (shared_gate ? shared_gate[t] : 1.0f);
         float v = 0.f;
         if (w != 0.f) {
             // an expert's block of the stacked product is its gate columns, then its up columns
             const int j = c - e * F;
             const T* block = gate_up + (size_t)t * gu_stride + 2 * (size_t)e * F;
-            v = silu(to_float(block[j])) * to_float(block[(e < E ? F : shared_ff) + j]) * w;
+            v = gated_inner(to_float(block[j]), to_float(block[(e < E ? F : shared_ff) + j]), w, form.kind,
+                            e < E ? form.limit : form.shared_limit, form.alpha);
         }
         inner[(size_t)t * inner_stride + c] = from_float<T>(v);
     }
@@ -393,11 +417,11 @@ moe_gather_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__
     for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = t < 0 ? from_float<T>(0.f) : src[c];
 }
 
-// inner[r, j] = silu(gate_up[r, j]) * gate_up[r, F + j] * row_weight[r]
+// inner[r, j] = silu(gate_up[r, j]) * gate_up[r, F + j] * row_weight[r], or the other form of GateForm
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_gate_mul_rows_kernel(const T* __restrict__ gate_up, int gu_stride, const float* __restrict__ row_weight,
-                         T* __restrict__ inner, int inner_stride, int rows, int F, int by8) {
+                         T* __restrict__ inner, int inner_stride, int rows, int F, int by8, GateForm form) {
     pdl_prologue();
     gate_up = pdl_fresh(gate_up);
     row_weight = pdl_fresh(row_weight);
@@ -415,7 +439,7 @@ moe_gate_mul_rows_kernel(const T* __restrict__ gate_up, int gu_stride, const flo
                 load8(row + j, g);
                 load8(row + F + j, u);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) v[k] = silu(g[k]) * u[k] * w;
+                for (int k = 0; k < 8; ++k) v[k] = gated_inner(g[k], u[k], w, form.kind, form.limit, form.alpha);
             }
             store8(inner + (size_t)r * inner_stride + j, v);
         }
@@ -428,7 +452,7 @@ moe_gate_mul_rows_kernel(const T* __restrict__ gate_up, int gu_stride, const flo
         float v = 0.f;
         if (w != 0.f) {
             const T* row = gate_up + (size_t)r * gu_stride;
-            v = silu(to_float(row[j])) * to_float(row[F + j]) * w;
+            v = gated_inner(to_float(row[j]), to_float(row[F + j]), w, form.kind, form.limit, form.alpha);
         }
         inner[(size_t)r * inner_stride + j] = from_float<T>(v);
     }
@@ -475,13 +499,14 @@ moe_combine_kernel(const float* __restrict__ down, int down_stride, const int* _
 PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int router_stride,
                            const void* shared_gate_w, float* dense, int* chosen, float* chosen_w, float* shared_gate,
                            int T, int W, int E, int top, int groups, int keep, int dtype, const float* raw,
-                           int raw_stride, const float* gain, float eps, void* stream) {
+                           int raw_stride, const float* gain, float eps, int score_kind, int normalize, void* stream) {
     if (T <= 0) return PS_OK;
     if (raw && !gain) return PS_ERR_BAD_ARGUMENT;
     if (W <= 0 || E <= 0 || top <= 0 || top > E || !x || !router || !dense || !chosen || !chosen_w)
         return PS_ERR_BAD_ARGUMENT;
     if (groups < 0 || (groups > 1 && (E % groups || keep <= 0 || keep > groups))) return PS_ERR_BAD_ARGUMENT;
     if (shared_gate_w && !shared_gate) return PS_ERR_BAD_ARGUMENT;
+    if (score_kind < 0 || score_kind > 1) return PS_ERR_BAD_ARGUMENT;
     if (E > ps::MOE_MAX_EXPERTS) return PS_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(T), block(ps::MOE_WARPS * 32);
@@ -493,12 +518,13 @@ PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int 
         return ps::launch_pdl(ps::moe_route_kernel<float>, grid, block, 0, s, (const float*)x, x_stride,
                               (const float*)router, router_stride, (const float*)shared_gate_w, dense, chosen,
                               chosen_w, shared_gate, T, W, E, top, groups, keep, by8, raw, raw_stride, gain, eps,
-                              (float*)const_cast<void*>(x));
+                              (float*)const_cast<void*>(x), score_kind, normalize);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_route_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)x,
                               x_stride, (const __nv_bfloat16*)router, router_stride,
                               (const __nv_bfloat16*)shared_gate_w, dense, chosen, chosen_w, shared_gate, T, W, E, top,
-                              groups, keep, by8, raw, raw_stride, gain, eps, (__nv_bfloat16*)const_cast<void*>(x));
+                              groups, keep, by8, raw, raw_stride, gain, eps, (__nv_bfloat16*)const_cast<void*>(x),
+                              score_kind, normalize);
     return PS_ERR_UNSUPPORTED;
 }
 
@@ -506,10 +532,11 @@ PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int 
 // columns from E * F on); inner [T, columns].
 PS_EXPORT int ps_moe_gate_mul(const void* gate_up, int gu_stride, const float* dense, const float* shared_gate,
                               void* inner, int inner_stride, int T, int columns, int E, int F, int dtype,
-                              void* stream) {
+                              int kind, float limit, float shared_limit, float alpha, void* stream) {
     if (T <= 0 || columns <= 0) return PS_OK;
     if (!gate_up || !inner || E < 0 || (E > 0 && !dense) || F <= 0 || columns < E * F) return PS_ERR_BAD_ARGUMENT;
-    if (columns > E * F && !shared_gate) return PS_ERR_BAD_ARGUMENT;
+    if (kind < 0 || kind > 1 || (kind == 1 && !(limit > 0.f && shared_limit > 0.f))) return PS_ERR_BAD_ARGUMENT;
+    const ps::GateForm form{kind, limit, shared_limit, alpha};
     cudaStream_t s = (cudaStream_t)stream;
     const int by8 = F % 8 == 0 && columns % 8 == 0 && gu_stride % 8 == 0 && inner_stride % 8 == 0 &&
                     !((uintptr_t)gate_up & 31) && !((uintptr_t)inner & 31);
@@ -518,11 +545,11 @@ PS_EXPORT int ps_moe_gate_mul(const void* gate_up, int gu_stride, const float* d
     const dim3 grid((unsigned)(blocks < 4736 ? blocks : 4736));
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::moe_gate_mul_kernel<float>, grid, dim3(256), 0, s, (const float*)gate_up, gu_stride,
-                              dense, shared_gate, (float*)inner, inner_stride, T, columns, E, F, by8);
+                              dense, shared_gate, (float*)inner, inner_stride, T, columns, E, F, by8, form);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_gate_mul_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
                               (const __nv_bfloat16*)gate_up, gu_stride, dense, shared_gate, (__nv_bfloat16*)inner,
-                              inner_stride, T, columns, E, F, by8);
+                              inner_stride, T, columns, E, F, by8, form);
     return PS_ERR_UNSUPPORTED;
 }
 
@@ -558,9 +585,12 @@ PS_EXPORT int ps_moe_gather(const void* x, int x_stride, const int* row_token, v
 
 // gate_up [R, 2 F] (gate columns, then up columns); row_weight float32 [R]; inner [R, F]
 PS_EXPORT int ps_moe_gate_mul_rows(const void* gate_up, int gu_stride, const float* row_weight, void* inner,
-                                   int inner_stride, int R, int F, int dtype, void* stream) {
+                                   int inner_stride, int R, int F, int dtype, int kind, float limit, float alpha,
+                                   void* stream) {
     if (R <= 0 || F <= 0) return PS_OK;
     if (!gate_up || !row_weight || !inner) return PS_ERR_BAD_ARGUMENT;
+    if (kind < 0 || kind > 1 || (kind == 1 && !(limit > 0.f))) return PS_ERR_BAD_ARGUMENT;
+    const ps::GateForm form{kind, limit, limit, alpha};
     cudaStream_t s = (cudaStream_t)stream;
     const int by8 = F % 8 == 0 && gu_stride % 8 == 0 && inner_stride % 8 == 0 && !((uintptr_t)gate_up & 31) &&
                     !((uintptr_t)inner & 31);
@@ -568,11 +598,11 @@ PS_EXPORT int ps_moe_gate_mul_rows(const void* gate_up, int gu_stride, const flo
     const dim3 grid((unsigned)(blocks < 4736 ? blocks : 4736));
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::moe_gate_mul_rows_kernel<float>, grid, dim3(256), 0, s, (const float*)gate_up,
-                              gu_stride, row_weight, (float*)inner, inner_stride, R, F, by8);
+                              gu_stride, row_weight, (float*)inner, inner_stride, R, F, by8, form);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_gate_mul_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
                               (const __nv_bfloat16*)gate_up, gu_stride, row_weight, (__nv_bfloat16*)inner, inner_stride,
-                              R, F, by8);
+                              R, F, by8, form);
     return PS_ERR_UNSUPPORTED;
 }
 

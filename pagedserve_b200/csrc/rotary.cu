@@ -140,7 +140,139 @@ rotary_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__
     }
 }
 
+
+// ---- the same step for heads that are normed before they turn ----
+// Per head, over its first `dim` numbers (a head occupies `head_dim` >= dim numbers of its row; what lies behind
+// `dim` is padding and is carried along unchanged):
+//     y = x / sqrt(mean(x^2) + eps) * gain          (gain float32 [dim], one for all query heads, one for all key
+//                                                    heads; a null gain: no norm)
+// then the first rot_dims numbers turn as above and the result goes back into q (queries) or into the key pages
+// (keys); the rows of v go into the value pages as they are.  k null: a layer that reads keys and values that
+// another layer cached; only its queries are prepared.  The angle p * f is formed to more than one float:
+// every frequency comes as (high, low) parts, the product's rounding error is recovered with an fma and what the
+// float that sincosf takes cannot hold is applied to first order.  Norm statistics, angles and products: float32.
+// One warp per head; a token's heads are shared out over gridDim.y CTAs.
+constexpr int HEAD_NORM_WARPS = 4;
+constexpr int HEAD_NORM_MAX_DIM = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(HEAD_NORM_WARPS * 32)
+head_norm_rotary_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                        const T* __restrict__ v, int v_stride, const float* __restrict__ q_gain,
+                        const float* __restrict__ k_gain, float eps, const float2* __restrict__ inv_freq, int rot_dims,
+                        int interleaved, const int* __restrict__ token_row, const int* __restrict__ positions,
+                        const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pool,
+                        T* __restrict__ v_pool, long long page_stride, int n_heads, int n_kv_heads, int head_dim,
+                        int dim, int page_size) {
+    __shared__ float2 turn[ROTARY_MAX_PAIRS];
+    __shared__ float staged[HEAD_NORM_WARPS][HEAD_NORM_MAX_DIM];
+    const int t = blockIdx.x;
+    const int p = positions[t];                              // static for the step: read before the wait
+    const int half = rot_dims >> 1;
+    const float pos = (float)p;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float2 f = inv_freq[i];
+        const float high = pos * f.x;
+        const float low = fmaf(pos, f.x, -high) + pos * f.y;
+        float sn, cs;
+        sincosf(high, &sn, &cs);
+        turn[i] = make_float2(fmaf(-low, sn, cs), fmaf(low, cs, sn));
+    }
+    pdl_prologue();
+    q = pdl_fresh(q);
+    k = pdl_fresh(k);
+    v = pdl_fresh(v);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_heads = n_heads + (k ? n_kv_heads : 0);
+    long long page_base = -1;
+    if (k && k_pool) {
+        const int page = block_table[(size_t)token_row[t] * bt_stride + p / page_size];
+        if (page >= 0) page_base = (long long)page * page_stride + (long long)(p % page_size) * head_dim;
+    }
+    float* mine = staged[warp];
+    for (int head = blockIdx.y * HEAD_NORM_WARPS + warp; head < total_heads; head += gridDim.y * HEAD_NORM_WARPS) {
+        const bool is_query = head < n_heads;
+        const int g = head - n_heads;
+        const T* src = is_query ? q + (size_t)t * q_stride + (size_t)head * head_dim
+                                : k + (size_t)t * k_stride + (size_t)g * head_dim;
+        const float* gain = is_query ? q_gain : k_gain;
+        float sq = 0.f;
+        for (int d = lane; d < dim; d += 32) {
+            const float x = to_float(src[d]);
+            mine[d] = x;
+            sq = fmaf(x, x, sq);
+        }
+        sq = warp_sum(sq);
+        const float inv = gain ? 1.0f / sqrtf(sq / (float)dim + eps) : 1.0f;
+        __syncwarp();
+        if (gain)
+            for (int d = lane; d < dim; d += 32) mine[d] = mine[d] * inv * gain[d];
+        __syncwarp();
+        T* dst = nullptr;
+        if (is_query) dst = q + (size_t)t * q_stride + (size_t)head * head_dim;
+        else if (page_base >= 0) dst = k_pool + page_base + (long long)g * page_size * head_dim;
+        if (dst) {
+            for (int unit = lane; unit < half; unit += 32) {
+                const int da = interleaved ? 2 * unit : unit, db = interleaved ? 2 * unit + 1 : unit + half;
+                const float a = mine[da], b = mine[db];
+                const float cs = turn[unit].x, sn = turn[unit].y;
+                dst[da] = from_float<T>(a * cs - b * sn);
+                dst[db] = from_float<T>(b * cs + a * sn);
+            }
+            for (int d = rot_dims + lane; d < dim; d += 32) dst[d] = from_float<T>(mine[d]);
+            if (!is_query) {
+                for (int d = dim + lane; d < head_dim; d += 32) dst[d] = src[d];
+                if (v) {
+                    const T* value = v + (size_t)t * v_stride + (size_t)g * head_dim;
+                    T* value_dst = v_pool + page_base + (long long)g * page_size * head_dim;
+                    for (int d = lane; d < head_dim; d += 32) value_dst[d] = value[d];
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
 }  // namespace ps
+
+// Heads that are normed, then turned (see head_norm_rotary_kernel).  q [T, n_heads * head_dim] in place; k, v
+// [T, n_kv_heads * head_dim] or both null (queries only); q_gain / k_gain float32 [dim] or null; inv_freq float32
+// [rot_dims / 2][2] as (high, low) parts; k_pool null: nothing is written to pages.
+PS_EXPORT int ps_head_norm_rotary_cache_write(void* q, int q_stride, const void* k, int k_stride, const void* v,
+                                              int v_stride, const float* q_gain, const float* k_gain, float eps,
+                                              const float* inv_freq, int rot_dims, int interleaved,
+                                              const int* token_row, const int* positions, const int* block_table,
+                                              int bt_stride, void* k_pool, void* v_pool, long long page_stride, int T,
+                                              int n_heads, int n_kv_heads, int head_dim, int dim, int page_size,
+                                              int dtype, void* stream) {
+    if (T <= 0) return PS_OK;
+    if (n_heads <= 0 || n_kv_heads < 0 || head_dim <= 0 || dim <= 0 || dim > head_dim || rot_dims < 0 ||
+        rot_dims > dim || (rot_dims & 1))
+        return PS_ERR_BAD_ARGUMENT;
+    if (rot_dims > 0 && (!inv_freq || ((uintptr_t)inv_freq & 7))) return PS_ERR_BAD_ARGUMENT;
+    if (rot_dims / 2 > ps::ROTARY_MAX_PAIRS || dim > ps::HEAD_NORM_MAX_DIM) return PS_ERR_UNSUPPORTED;
+    if (!positions || !q || (k && !v) || (!k && v)) return PS_ERR_BAD_ARGUMENT;
+    if (k && k_pool && (!v_pool || !token_row || !block_table || page_size <= 0)) return PS_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int heads = n_heads + (k ? n_kv_heads : 0);
+    int split = (heads + ps::HEAD_NORM_WARPS - 1) / ps::HEAD_NORM_WARPS;
+    if (T >= 2048 && split > 2) split = 2;                   // many tokens: fewer CTAs, each walks several heads
+    const dim3 grid(T, split), block(ps::HEAD_NORM_WARPS * 32);
+    if (dtype == PS_F32)
+        return ps::launch_pdl(ps::head_norm_rotary_kernel<float>, grid, block, 0, s, (float*)q, q_stride,
+                              (const float*)k, k_stride, (const float*)v, v_stride, q_gain, k_gain, eps,
+                              (const float2*)inv_freq, rot_dims, interleaved, token_row, positions, block_table,
+                              bt_stride, (float*)k_pool, (float*)v_pool, page_stride, n_heads, n_kv_heads, head_dim,
+                              dim, page_size);
+    if (dtype == PS_BF16)
+        return ps::launch_pdl(ps::head_norm_rotary_kernel<__nv_bfloat16>, grid, block, 0, s, (__nv_bfloat16*)q,
+                              q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_gain,
+                              k_gain, eps, (const float2*)inv_freq, rot_dims, interleaved, token_row, positions,
+                              block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride,
+                              n_heads, n_kv_heads, head_dim, dim, page_size);
+    return PS_ERR_UNSUPPORTED;
+}
 
 // q [T, n_heads * head_dim] is turned in place. k [T, n_kv_heads * head_dim] is read only. v may be null: the
 // values are then the keys as projected. k_pool null: nothing is written to pages (queries only).

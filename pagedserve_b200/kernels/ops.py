@@ -91,11 +91,13 @@ _SIGNATURES = {
         "ps_latent_prepare": [_P, _I, _P, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _L, _I, _P, _I, _I, _I, _I, _I, _I,
                               _I, _P],
         "ps_sigmoid_gate": [_P, _I, _P, _I, _I, _I, _I, _P],
-        "ps_moe_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _F, _P],
-        "ps_moe_gate_mul": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "ps_moe_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _F, _I, _I, _P],
+        "ps_moe_gate_mul": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+        "ps_head_norm_rotary_cache_write": [_P, _I, _P, _I, _P, _I, _P, _P, _F, _P, _I, _I, _P, _P, _P, _I, _P, _P, _L,
+                                            _I, _I, _I, _I, _I, _I, _I, _P],
         "ps_moe_plan": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P],
         "ps_moe_gather": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
-        "ps_moe_gate_mul_rows": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
+        "ps_moe_gate_mul_rows": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
         "ps_moe_combine": [_P, _I, _P, _I, _P, _I, _I, _I, _P],
         "ps_step_shape": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
         "ps_step_fill": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _P, _I, _I, _I, _I, _P],
@@ -737,7 +739,8 @@ class Ops:
         if (q.shape[1] != heads * head_dim or out.shape != q.shape or not q.is_contiguous()
                 or not out.is_contiguous()):
             raise KernelError("shared_position_attention: q and out must be contiguous [T, heads * head_dim]")
-        seen = min(max_kv_len, window) if (window and max_kv_len) else (max_kv_len or window or 0)
+        extent = abs(window or 0)                                     # a chunked mask (negative) bounds the keys alike
+        seen = min(max_kv_len, extent) if (extent and max_kv_len) else (max_kv_len or extent or 0)
         tiles = -(-seen // 64) + 1 if seen else 1                      # 64-key tiles a token can touch
         splits = max(1, min(8, 296 // max(T, 1), tiles)) if heads <= 64 else 1
         partial = self.empty((T * splits * heads * (head_dim + 2),), torch.float32, q.device) if splits > 1 else None
@@ -781,9 +784,16 @@ class Ops:
         return out
 
     def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale,
-                  write_cache=True, softcap=None, sink=None):
+                  write_cache=True, softcap=None, sink=None, chunk=None):
         """Write the step's keys and values into the pages, then attend from the pages.  ``softcap`` and
-        ``sink`` as in :meth:`paged_attention_simt`."""
+        ``sink`` as in :meth:`paged_attention_simt`.  Besides "no later key", a query sees the last ``window``
+        keys, or (``chunk`` C instead of a window) the keys j of its own run of C positions,
+        ``j // C == i // C``, runs counted from position 0 of the sequence; neither: every earlier key.  Below
+        this method the two travel as one integer: the window, or minus the chunk."""
+        if chunk:
+            if window:
+                raise KernelError("attention: a window or a chunked mask, not both")
+            window = -int(chunk)
         if write_cache:
             self.kv_append(k, v, ctx.token_slot, ctx.positions, layer.block_table, layer.k_pool, layer.v_pool,
                            layer.page_stride, n_kv_heads, head_dim, layer.page_size)
@@ -830,6 +840,48 @@ class Ops:
             _ptr(layer.k_pool) if pools else None, _ptr(layer.v_pool) if pools else None,
             layer.page_stride if pools else 0, T, n_heads, n_kv_heads, head_dim,
             layer.page_size if pools else 1, self.code, _stream()), "rotary_cache_write")
+
+    def head_norm_rotary_cache_write(self, q, k, v, q_gain, k_gain, eps, inv_freq, rot_dims, interleaved, dim, ctx,
+                                     layer, n_heads, n_kv_heads, head_dim, write_cache=True):
+        """As :meth:`rotary_cache_write` for heads that are normed before they turn: per head, its first ``dim``
+        numbers (of ``head_dim``; the rest is padding) are divided by their root mean square (eps inside the root)
+        and multiplied by ``q_gain`` / ``k_gain`` (float32 [dim], one for all heads of a kind; None: no norm), then
+        the first ``rot_dims`` turn.  Queries in place, keys into the key pages, the rows of ``v`` into the value
+        pages.  ``k`` and ``v`` None: a layer that reads another layer's cache prepares its queries only.
+        ``inv_freq``: float32 [rot_dims / 2, 2] as (high, low) parts (``RotaryPositions.inv_freq_split``)."""
+        T = q.shape[0]
+        _require(q, "q", self.dtype)
+        if (k is None) != (v is None):
+            raise KernelError("head_norm_rotary: keys and values come together")
+        for name, tensor in (("k", k), ("v", v)):
+            if tensor is not None:
+                _require(tensor, name, self.dtype)
+                if tensor.stride(1) != 1 or tensor.shape[1] != n_kv_heads * head_dim:
+                    raise KernelError("head_norm_rotary: keys and values must be rows of n_kv_heads * head_dim")
+        for name, gain in (("q_gain", q_gain), ("k_gain", k_gain)):
+            if gain is not None:
+                _require(gain, name, torch.float32)
+                if gain.numel() != dim or not gain.is_contiguous():
+                    raise KernelError("head_norm_rotary: one gain per normed dimension")
+        if rot_dims:
+            _require(inv_freq, "inv_freq", torch.float32)
+            if inv_freq.shape != (rot_dims // 2, 2) or not inv_freq.is_contiguous():
+                raise KernelError("head_norm_rotary: one (high, low) frequency per pair of turning dimensions")
+        if q.stride(1) != 1 or q.shape[1] != n_heads * head_dim:
+            raise KernelError("head_norm_rotary: queries must be rows of n_heads * head_dim")
+        pools = write_cache and k is not None and layer is not None and layer.k_pool is not None
+        if pools:
+            _require(layer.k_pool, "k_pool", self.dtype)
+        self.launches += 1
+        _check(self.core.ps_head_norm_rotary_cache_write(
+            _ptr(q), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0, _ptr(v),
+            v.stride(0) if v is not None else 0, _ptr(q_gain), _ptr(k_gain), float(eps),
+            _ptr(inv_freq) if rot_dims else None, rot_dims, 1 if interleaved else 0,
+            _ptr(ctx.token_slot) if pools else None, _ptr(ctx.positions),
+            _ptr(layer.block_table) if pools else None, layer.block_table.stride(0) if pools else 0,
+            _ptr(layer.k_pool) if pools else None, _ptr(layer.v_pool) if pools else None,
+            layer.page_stride if pools else 0, T, n_heads, n_kv_heads, head_dim, dim,
+            layer.page_size if pools else 1, self.code, _stream()), "head_norm_rotary_cache_write")
 
     # ------------------------------------------------------------------ linear recurrence with decay ("wkv")
     def token_shift_mix(self, x, mu, state, prev_offset, ctx, out):
@@ -1007,14 +1059,18 @@ class Ops:
         return heads
 
     # ------------------------------------------------------------------ routed experts
-    def moe_route(self, x, router, shared_gate_w, dense, chosen, chosen_w, shared_gate, top, groups, keep, norm=None):
+    def moe_route(self, x, router, shared_gate_w, dense, chosen, chosen_w, shared_gate, top, groups, keep, norm=None,
+                  score="softmax", normalize=True):
         """The router of a layer of experts (csrc/moe.cu): softmax of ``x @ router.T`` in float32, the ``top``
         largest among the experts of the ``keep`` best of ``groups`` groups (0 or 1 groups: all experts stand),
         weights normalised to sum 1.  ``dense`` float32 [T, E] gets the weights (0 where not chosen), ``chosen``
         int32 / ``chosen_w`` float32 [T, top] the election, ``shared_gate`` float32 [T] = sigmoid(x . shared_gate_w)
         where ``shared_gate_w`` [W] is given.  ``norm`` = (raw float32 [T, W], gain float32 [W], eps): the kernel
         first writes the RMS norm of ``raw`` into ``x`` (the rows the experts' products then read) instead of
-        reading ``x``."""
+        reading ``x``.  ``score`` "sigmoid": the scores are sigmoid(z) expert by expert instead of the softmax;
+        ``normalize`` False: the weights are the chosen scores themselves."""
+        if score not in ("softmax", "sigmoid"):
+            raise KernelError(f"moe_route: unknown score {score!r}")
         T, W = x.shape
         E = router.shape[0]
         _require(x, "x", self.dtype)
@@ -1043,29 +1099,42 @@ class Ops:
         _check(self.core.ps_moe_route(_ptr(x), x.stride(0), _ptr(router), router.stride(0), _ptr(shared_gate_w),
                                       _ptr(dense), _ptr(chosen), _ptr(chosen_w), _ptr(shared_gate), T, W, E, top,
                                       int(groups or 0), int(keep or 0), self.code, _ptr(raw),
-                                      raw.stride(0) if raw is not None else 0, _ptr(gain), float(eps), _stream()),
+                                      raw.stride(0) if raw is not None else 0, _ptr(gain), float(eps),
+                                      1 if score == "sigmoid" else 0, 1 if normalize else 0, _stream()),
                "moe_route")
 
-    def moe_gate_mul(self, gate_up, dense, shared_gate, inner, n_experts, expert_ff):
+    @staticmethod
+    def _gate_form(form):
+        """(kind, limit, shared limit, alpha) of the inner activation: None / "silu" = silu(g) * u * weight;
+        ("clamped_swish", limit, shared_limit, alpha): g' = min(weight * g, limit), u' = clamp(weight * u, +-limit),
+        g' * sigmoid(alpha * g') * (u' + 1): the weight scales the expert's input."""
+        if form is None or form == "silu":
+            return 0, 0.0, 0.0, 0.0
+        kind, limit, shared_limit, alpha = form
+        if kind != "clamped_swish":
+            raise KernelError(f"unknown gated form {kind!r}")
+        return 1, float(limit), float(shared_limit if shared_limit is not None else limit), float(alpha)
+
+    def moe_gate_mul(self, gate_up, dense, shared_gate, inner, n_experts, expert_ff, form=None):
         """inner[t, c] = silu(gate) * up * weight over the stacked product ``gate_up`` [T, 2 C], C = inner.shape[1]:
         expert e's block of 2 * expert_ff columns is its gates, then its ups, and the shared expert's block follows;
         the weight of inner's column c is ``dense[t, c // expert_ff]`` for the experts' columns and
-        ``shared_gate[t]`` from column ``n_experts * expert_ff`` on (csrc/moe.cu).  ``n_experts`` 0: the product of a
-        shared expert alone."""
+        ``shared_gate[t]`` (None: 1) from column ``n_experts * expert_ff`` on (csrc/moe.cu).  ``n_experts`` 0: the
+        product of a shared expert alone, or of a dense gated feed-forward.  ``form``: see :meth:`_gate_form`."""
         T, C = inner.shape
         _require(gate_up, "gate_up", self.dtype)
         _require(inner, "inner", self.dtype)
-        _require(dense, "dense", torch.float32)
         if (gate_up.shape != (T, 2 * C) or gate_up.stride(1) != 1 or inner.stride(1) != 1
                 or (n_experts and (dense.shape != (T, n_experts) or not dense.is_contiguous()))):
             raise KernelError("moe_gate_mul: shapes do not match")
+        if n_experts:
+            _require(dense, "dense", torch.float32)
         if shared_gate is not None:
             _require(shared_gate, "shared_gate", torch.float32)
-        elif C > n_experts * expert_ff:
-            raise KernelError("moe_gate_mul: columns of a shared expert need its gate")
         self.launches += 1
-        _check(self.core.ps_moe_gate_mul(_ptr(gate_up), gate_up.stride(0), _ptr(dense), _ptr(shared_gate), _ptr(inner),
-                                         inner.stride(0), T, C, n_experts, expert_ff, self.code, _stream()),
+        _check(self.core.ps_moe_gate_mul(_ptr(gate_up), gate_up.stride(0), _ptr(dense) if n_experts else None,
+                                         _ptr(shared_gate), _ptr(inner), inner.stride(0), T, C, n_experts, expert_ff,
+                                         self.code, *self._gate_form(form), _stream()),
                "moe_gate_mul")
         return inner
 
@@ -1107,8 +1176,9 @@ class Ops:
                                        rows.shape[0], x.shape[1], self.code, _stream()), "moe_gather")
         return rows
 
-    def moe_gate_mul_rows(self, gate_up, row_weight, inner):
-        """inner[r, j] = silu(gate_up[r, j]) * gate_up[r, F + j] * row_weight[r]."""
+    def moe_gate_mul_rows(self, gate_up, row_weight, inner, form=None):
+        """inner[r, j] = silu(gate_up[r, j]) * gate_up[r, F + j] * row_weight[r], or the other ``form`` of
+        :meth:`_gate_form` (with the routed experts' limit)."""
         R, F = inner.shape
         _require(gate_up, "gate_up", self.dtype)
         _require(inner, "inner", self.dtype)
@@ -1116,8 +1186,10 @@ class Ops:
         if gate_up.shape != (R, 2 * F) or row_weight.numel() != R or gate_up.stride(1) != 1 or inner.stride(1) != 1:
             raise KernelError("moe_gate_mul_rows: shapes do not match")
         self.launches += 1
+        kind, limit, _, alpha = self._gate_form(form)
         _check(self.core.ps_moe_gate_mul_rows(_ptr(gate_up), gate_up.stride(0), _ptr(row_weight), _ptr(inner),
-                                              inner.stride(0), R, F, self.code, _stream()), "moe_gate_mul_rows")
+                                              inner.stride(0), R, F, self.code, kind, limit, alpha, _stream()),
+               "moe_gate_mul_rows")
         return inner
 
     def moe_combine(self, down, row_of, top, y):

@@ -93,7 +93,12 @@ class Model:
         for entry in self.spec.schedule:
             need = getattr(self.blocks[entry.layer].mixer, which)()
             if seen[entry.cache_layer] and needs[entry.cache_layer] != need:
-                raise ValueError(f"cache layer {entry.cache_layer} is shared by runs with different needs")
+                # runs that read the same rows through different masks: the rows stay for the longer look back
+                both = needs[entry.cache_layer]
+                merge = getattr(both, "merged", None) if need is not None else None
+                need = merge(need) if merge is not None else None
+                if need is None:
+                    raise ValueError(f"cache layer {entry.cache_layer} is shared by runs with different needs")
             needs[entry.cache_layer] = need
             seen[entry.cache_layer] = True
         return needs

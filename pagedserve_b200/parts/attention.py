@@ -100,18 +100,30 @@ class CausalSelfAttention(Mixer):
 class RotaryAttention(Mixer):
     """Attention with separate projections, rotary positions of its own, and optional extras of the softmax.
 
-    q = x W_q, k = x W_k, v = x W_v, or, without ``v_name``, v = k as projected (before it is turned): such a
-    layer has no value projection.  Queries and keys turn by position (``rotary``: dims, base, interleaved);
-    s = (q . k) * scale; with ``softcap`` c: s <- c * tanh(s / c); query i sees keys j with
-    0 <= i - j < ``window`` (all earlier keys without a window); with ``sink_name`` every query head has a
-    learned number whose exponential is added to the softmax's denominator and to nothing else;
-    residual += o W_o.  Scores, softmax, angles: float32.
+    q = x W_q, k = x W_k, v = x W_v (each plus a bias with ``bias``), or, without ``v_name``, v = k as projected
+    (before it is turned): such a layer has no value projection.  With ``head_norm`` every query head and every key
+    head is first divided by its root mean square (eps inside the root) and multiplied by a gain of ``head_dim``
+    numbers, one gain for all query heads and one for all key heads.  Queries and keys then turn by position
+    (``rotary``: dims, base, interleaved);
+    s = (q . k) * scale; with ``softcap`` c: s <- c * tanh(s / c); query i sees keys j <= i with
+    i - j < ``window``, or, with ``chunk`` C instead, with j // C == i // C (runs of C positions counted from
+    position 0 of the sequence, however the prompt was cut); neither: all earlier keys.  With ``sink_name`` every
+    query head has a learned number whose exponential is added to the softmax's denominator and to nothing else;
+    values may have a size of their own (``v_dim``); residual += o W_o.  Scores, softmax, norms, angles: float32.
 
-    The projections run as one product over the stacked matrices; one kernel then turns the queries in place
-    and sends the turned keys and the values into the pages; attention reads only pages.
+    ``kv_source`` False: the layer has no key and value tensors (projections, biases, key gain); its run in the
+    schedule names the cache layer of another layer, which has written that step's keys and values (after their
+    norm and turning) before this one runs, and it brings only its own queries, mask and output projection.
 
-    params: hidden_size, n_heads, n_kv_heads, head_dim, scale, window, softcap, rotary (dict or None),
-    q_name, k_name, v_name (None: values are the unturned keys), out_name, sink_name (None: no sinks),
+    The projections run as one product over the stacked matrices; one kernel then norms and turns the queries in
+    place and sends the keys and the values into the pages; attention reads only pages.  Where a layer with a value
+    projection has key and value sizes that differ, or that are no multiple of 16 in bfloat16, a cached head takes
+    ``slot_dim`` numbers, the larger of the two rounded up: the projections' matrices get zero rows there (zero keys add nothing to a score, zero values
+    give zeros that the output projection's zero columns ignore), and every attention kernel runs unchanged.
+
+    params: hidden_size, n_heads, n_kv_heads, head_dim, v_dim (head_dim), scale, window, chunk, softcap,
+    rotary (dict or None), q_name, k_name, v_name (None: values are the unturned keys), out_name, sink_name (None: no
+    sinks), bias (False; tensors ``<name>.b``), head_norm (None, or dict(q_name, k_name, eps)), kv_source (True),
     init_std, out_init_std.
     """
 
@@ -123,13 +135,30 @@ class RotaryAttention(Mixer):
         p = self.params
         if p["n_heads"] % p["n_kv_heads"] != 0:
             raise ValueError("n_heads must be a multiple of n_kv_heads")
-        if not (0 < p["head_dim"] <= 256):
-            raise ValueError(f"head_dim {p['head_dim']} is not supported: at most 256")
+        self.dim = p["head_dim"]
+        self.v_dim = p.get("v_dim") or self.dim
+        self.has_v = p.get("v_name") is not None
+        self.kv_source = p.get("kv_source", True)
+        self.head_norm = p.get("head_norm")
+        if not self.has_v and self.v_dim != self.dim:
+            raise ValueError("values that are the unturned keys have the keys' size")
+        # what a head takes in the cache and in the attention kernels
+        slot = max(self.dim, self.v_dim)
+        if env.dtype == torch.bfloat16 and self.has_v:
+            slot = -(-slot // 16) * 16                 # the tensor-core attention kernels take multiples of 16
+        self.slot_dim = slot
+        if not (0 < self.slot_dim <= 256):
+            raise ValueError(f"head_dim {p['head_dim']} / v_dim {self.v_dim} is not supported: at most 256")
         if p.get("window") is not None and p["window"] <= 0:
             raise ValueError("window must be positive")
-        self.q_width = p["n_heads"] * p["head_dim"]
-        self.kv_width = p["n_kv_heads"] * p["head_dim"]
-        self.has_v = p.get("v_name") is not None
+        if p.get("chunk") is not None and (p["chunk"] <= 0 or p.get("window") is not None):
+            raise ValueError("chunk must be positive, and excludes a window")
+        # the plain kernel turns heads as they are; norms, padded heads and borrowed keys take the other one
+        self.plain = (self.head_norm is None and self.slot_dim == self.dim == self.v_dim and self.kv_source)
+        if not self.plain and not self.has_v:
+            raise ValueError("rotary_attention: head norms, padded heads and borrowed keys need a value projection")
+        self.q_width = p["n_heads"] * self.slot_dim
+        self.kv_width = p["n_kv_heads"] * self.slot_dim
         rotary = p.get("rotary") or dict(dims=0, base=10000.0)
         from pagedserve_b200.parts.positions import RotaryPositions
 
@@ -139,45 +168,89 @@ class RotaryAttention(Mixer):
 
     def cache_need(self):
         p = self.params
-        return KVNeed(p["n_kv_heads"], p["head_dim"], p.get("window"))
+        return KVNeed(p["n_kv_heads"], self.slot_dim, p.get("window"), chunk=p.get("chunk"))
 
     def param_specs(self):
         p = self.params
+        W, H, G = p["hidden_size"], p["n_heads"], p["n_kv_heads"]
         std = p.get("init_std", 0.02)
-        specs = [(ParamSpec(self._n(p["q_name"]), (self.q_width, p["hidden_size"]), "matmul"), ("normal", std)),
-                 (ParamSpec(self._n(p["k_name"]), (self.kv_width, p["hidden_size"]), "matmul"), ("normal", std))]
-        if self.has_v:
-            specs.append((ParamSpec(self._n(p["v_name"]), (self.kv_width, p["hidden_size"]), "matmul"),
-                          ("normal", std)))
-        specs.append((ParamSpec(self._n(p["out_name"]), (p["hidden_size"], self.q_width), "matmul"),
+        names = [(p["q_name"], H * self.dim)]
+        if self.kv_source:
+            names.append((p["k_name"], G * self.dim))
+            if self.has_v:
+                names.append((p["v_name"], G * self.v_dim))
+        specs = [(ParamSpec(self._n(name), (rows, W), "matmul"), ("normal", std)) for name, rows in names]
+        if p.get("bias"):
+            specs += [(ParamSpec(self._n(name + ".b"), (rows,), "vector"), ("normal", 0.3)) for name, rows in names]
+        if self.head_norm:
+            specs.append((ParamSpec(self._n(self.head_norm["q_name"]), (self.dim,), "vector"), ("ones_plus_normal", 0.1)))
+            if self.kv_source:
+                specs.append((ParamSpec(self._n(self.head_norm["k_name"]), (self.dim,), "vector"),
+                              ("ones_plus_normal", 0.1)))
+        specs.append((ParamSpec(self._n(p["out_name"]), (W, H * self.v_dim), "matmul"),
                       ("normal", p.get("out_init_std", std))))
         if p.get("sink_name"):
-            specs.append((ParamSpec(self._n(p["sink_name"]), (p["n_heads"],), "vector"), ("normal", 1.0)))
+            specs.append((ParamSpec(self._n(p["sink_name"]), (H,), "vector"), ("normal", 1.0)))
         return specs
+
+    def _padded_rows(self, tensor, heads, size):
+        """[heads * size, ...] -> [heads * slot_dim, ...] with zero rows behind every head's own."""
+        if size == self.slot_dim:
+            return tensor
+        shaped = tensor.reshape(heads, size, *tensor.shape[1:])
+        out = shaped.new_zeros((heads, self.slot_dim) + tuple(tensor.shape[1:]))
+        out[:, :size] = shaped
+        return out.reshape(heads * self.slot_dim, *tensor.shape[1:])
 
     def bind(self, tensors):
         p = self.params
-        pieces = [tensors[self._n(p["q_name"])], tensors[self._n(p["k_name"])]]
-        if self.has_v:
-            pieces.append(tensors[self._n(p["v_name"])])
-        self.w_in = torch.cat(pieces, dim=0).contiguous()              # [q + k (+ v), H]
-        self.w_out = tensors[self._n(p["out_name"])]
+        H, G = p["n_heads"], p["n_kv_heads"]
+        kinds = [(p["q_name"], H, self.dim)]
+        if self.kv_source:
+            kinds.append((p["k_name"], G, self.dim))
+            if self.has_v:
+                kinds.append((p["v_name"], G, self.v_dim))
+        self.w_in = torch.cat([self._padded_rows(tensors[self._n(name)], heads, size) for name, heads, size in kinds],
+                              dim=0).contiguous()                   # [q + k (+ v), W]
+        self.b_in = None
+        if p.get("bias"):
+            self.b_in = torch.cat([self._padded_rows(tensors[self._n(name + ".b")], heads, size)
+                                   for name, heads, size in kinds], dim=0).contiguous()
+        w_out = tensors[self._n(p["out_name"])]
+        if self.v_dim != self.slot_dim:                             # zero columns where the heads are padded
+            w_out = self._padded_rows(w_out.t().contiguous(), H, self.v_dim).t().contiguous()
+        self.w_out = w_out
         self.sink = tensors[self._n(p["sink_name"])].contiguous() if p.get("sink_name") else None
+        self.q_gain = self.k_gain = None
+        if self.head_norm:
+            self.q_gain = tensors[self._n(self.head_norm["q_name"])].contiguous()
+            if self.kv_source:
+                self.k_gain = tensors[self._n(self.head_norm["k_name"])].contiguous()
 
     def forward(self, x, residual, ctx, layer):
         p = self.params
         ops = self.env.ops
         tokens = x.shape[0]
+        H, G, D = p["n_heads"], p["n_kv_heads"], self.slot_dim
         projected = ops.empty((tokens, self.w_in.shape[0]), self.env.dtype, residual.device)
-        ops.linear(x, self.w_in, None, projected)
+        ops.linear(x, self.w_in, self.b_in, projected)
         q = projected[:, :self.q_width]
-        k = projected[:, self.q_width:self.q_width + self.kv_width]
-        v = projected[:, self.q_width + self.kv_width:] if self.has_v else None
-        self.rotary.turn_and_store(q, k, v, ctx, layer, p["n_heads"], p["n_kv_heads"],
-                                   write_cache=p.get("write_cache", True))
+        k = v = None
+        if self.kv_source:
+            k = projected[:, self.q_width:self.q_width + self.kv_width]
+            v = projected[:, self.q_width + self.kv_width:] if self.has_v else None
+        write_cache = p.get("write_cache", True) and self.kv_source
+        if self.plain:
+            self.rotary.turn_and_store(q, k, v, ctx, layer, H, G, write_cache=write_cache)
+        else:
+            rotary = self.rotary.params
+            ops.head_norm_rotary_cache_write(
+                q, k, v, self.q_gain, self.k_gain, float(self.head_norm["eps"]) if self.head_norm else 0.0,
+                self.rotary.inv_freq_split(), rotary["dims"], rotary.get("interleaved", True), self.dim, ctx, layer,
+                H, G, D, write_cache=write_cache)
         context = ops.empty((tokens, self.q_width), self.env.dtype, residual.device)
-        ops.attention(q, k, v, context, ctx, layer, p["n_heads"], p["n_kv_heads"], p["head_dim"], p.get("window"),
-                      float(p["scale"]), write_cache=False, softcap=p.get("softcap"), sink=self.sink)
+        ops.attention(q, k, v, context, ctx, layer, H, G, D, p.get("window"), float(p["scale"]), write_cache=False,
+                      softcap=p.get("softcap"), sink=self.sink, chunk=p.get("chunk"))
         ops.linear(context, self.w_out, None, residual, accumulate=True)
 
 

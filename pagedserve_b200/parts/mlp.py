@@ -13,10 +13,12 @@ ACTIVATIONS = ("gelu_tanh", "gelu_erf", "relu_squared", "silu")
 @register_part("feed_forward", "dense_mlp")
 class DenseMLP(FeedForward):
     """residual += act(x W_up + b_up) W_down + b_down
-    (reference: src/model/paged_decoder.py:178-179, 224-228, 273-280).
+    (reference: src/model/paged_decoder.py:178-179, 224-228, 273-280),
+    or, with ``gate_name``, the gated form residual += (act(x W_gate) * (x W_up)) W_down (activation 'silu', no
+    biases): gate and up run as one product over the stacked matrices, one elementwise kernel forms the inner row.
     params: hidden_size, inner_size, activation ('gelu_tanh' | 'gelu_erf' | 'relu_squared' = max(z, 0)^2 | 'silu'),
     has_bias,
-    stored_in_out, up_name, down_name, init_std, out_init_std."""
+    stored_in_out, up_name, down_name, gate_name (None), init_std, out_init_std."""
 
     graph_safe = True
     accepts_deferred_norm = True       # x goes straight into ops.linear
@@ -25,6 +27,8 @@ class DenseMLP(FeedForward):
         super().__init__(params, prefix, env)
         if self.params["activation"] not in ACTIVATIONS:
             raise ValueError(f"unsupported activation {self.params['activation']!r}; one of {ACTIVATIONS}")
+        if self.params.get("gate_name") and (self.params["activation"] != "silu" or self.params.get("has_bias", True)):
+            raise ValueError("dense_mlp: the gated form is silu(gate) * up without biases")
 
     def _matrix(self, name, n_out, n_in, std):
         flip = self.params.get("stored_in_out", False)
@@ -35,6 +39,8 @@ class DenseMLP(FeedForward):
         p = self.params
         specs = [self._matrix(p["up_name"], p["inner_size"], p["hidden_size"], p.get("init_std", 0.02)),
                  self._matrix(p["down_name"], p["hidden_size"], p["inner_size"], p.get("out_init_std", 0.02))]
+        if p.get("gate_name"):
+            specs.insert(0, self._matrix(p["gate_name"], p["inner_size"], p["hidden_size"], p.get("init_std", 0.02)))
         if p.get("has_bias", True):
             specs.append((ParamSpec(self._n(p["up_name"] + ".bias"), (p["inner_size"],), "vector"),
                           ("normal", p.get("init_std", 0.02))))
@@ -49,12 +55,20 @@ class DenseMLP(FeedForward):
         has_bias = p.get("has_bias", True)
         self.b_up = tensors[self._n(p["up_name"] + ".bias")] if has_bias else None
         self.b_down = tensors[self._n(p["down_name"] + ".bias")] if has_bias else None
+        self.w_gate_up = None
+        if p.get("gate_name"):
+            self.w_gate_up = torch.cat([tensors[self._n(p["gate_name"] + ".weight")], self.w_up], dim=0).contiguous()
 
     def forward(self, x, residual, ctx):
         p = self.params
         ops = self.env.ops
         inner = ops.empty((x.shape[0], p["inner_size"]), self.env.dtype, x.device)
-        ops.linear(x, self.w_up, self.b_up, inner, act=p["activation"])
+        if self.w_gate_up is not None:
+            gate_up = ops.empty((x.shape[0], 2 * p["inner_size"]), self.env.dtype, x.device)
+            ops.linear(x, self.w_gate_up, None, gate_up)
+            ops.moe_gate_mul(gate_up, None, None, inner, 0, p["inner_size"])
+        else:
+            ops.linear(x, self.w_up, self.b_up, inner, act=p["activation"])
         ops.linear(inner, self.w_down, self.b_down, residual, accumulate=True)
 
 

@@ -17,7 +17,14 @@ class RoutedExperts(FeedForward):
     is its largest s, and only experts of the ``group_keep`` groups with the largest marks can be chosen (no
     groups: all can); the ``top`` largest s among them are chosen and their weights are s over the sum of the
     chosen s (+ 1e-20).  A shared expert of the same form (its own inner size) runs for every token, multiplied by
-    sigmoid(w_sg . x), one number per token.
+    sigmoid(w_sg . x), one number per token (``shared_gate`` False: the shared expert is added as it is).
+
+    Other forms of the same part.  ``score`` "sigmoid": s = sigmoid(z), expert by expert, instead of the softmax;
+    ``normalize`` False: the weights are the chosen s themselves.  ``expert_form`` dict(kind="clamped_swish", limit,
+    alpha): an expert is W_down (g sigmoid(alpha g) (u + 1)) with g = min(W_gate x', limit), u = clamp(W_up x',
+    -limit, limit), and its weight multiplies its input, x' = w x, not its output; the shared expert has a limit of
+    its own (``shared_limit``).  There are no biases, so W (w x) = w (W x): the weight is applied to the two
+    pre-activations in float32 by the kernel that forms the inner row, in both ways of running.
 
     How it runs.  The gate and up matrices of all experts (and of the shared one) are stacked into one matrix,
     expert by expert, and the down matrices stand side by side along their inner axis; the weight multiplies the
@@ -34,6 +41,7 @@ class RoutedExperts(FeedForward):
     sums up to their order.
 
     params: hidden_size, n_experts, expert_ff, top, groups, group_keep, shared_ff (None: no shared expert),
+    score ("softmax"), normalize (True), expert_form (None: silu), shared_limit, shared_gate (True),
     init_std, out_init_std; tensors ``router``, ``e<i>.gate / up / down``, ``shared.gate / up / down / sg``.
     """
 
@@ -50,6 +58,16 @@ class RoutedExperts(FeedForward):
         if groups > 1 and (E % groups or not (0 < (p.get("group_keep") or 0) <= groups)):
             raise ValueError("routed_experts: groups must divide the experts, and 0 < group_keep <= groups")
         self.columns = E * p["expert_ff"] + (p.get("shared_ff") or 0)
+        if p.get("score", "softmax") not in ("softmax", "sigmoid"):
+            raise ValueError("routed_experts: score is 'softmax' or 'sigmoid'")
+        form = p.get("expert_form")
+        self.form = None
+        if form is not None and form.get("kind", "silu") != "silu":
+            if form["kind"] != "clamped_swish" or not form["limit"] > 0:
+                raise ValueError("routed_experts: expert_form is silu, or clamped_swish with a positive limit")
+            self.form = ("clamped_swish", float(form["limit"]), float(p.get("shared_limit") or form["limit"]),
+                         float(form.get("alpha", 1.702)))
+        self.has_shared_gate = bool(p.get("shared_ff")) and p.get("shared_gate", True)
 
     def _expert_names(self):
         names = [f"e{index}." for index in range(self.params["n_experts"])]
@@ -65,7 +83,7 @@ class RoutedExperts(FeedForward):
             specs += [(ParamSpec(self._n(name + "gate"), (F, W), "matmul"), ("normal", std)),
                       (ParamSpec(self._n(name + "up"), (F, W), "matmul"), ("normal", std)),
                       (ParamSpec(self._n(name + "down"), (W, F), "matmul"), ("normal", out_std))]
-        if p.get("shared_ff"):
+        if self.has_shared_gate:
             specs.append((ParamSpec(self._n("shared.sg"), (1, W), "matmul"), ("normal", std)))
         return specs
 
@@ -76,7 +94,7 @@ class RoutedExperts(FeedForward):
         self.w_gate_up = torch.cat([t(name + which) for name in names for which in ("gate", "up")],
                                    dim=0).contiguous()           # [2 * columns, W]: per expert its gates, then its ups
         self.w_down = torch.cat([t(name + "down") for name in names], dim=1).contiguous()      # [W, columns]
-        self.w_shared_gate = t("shared.sg").reshape(-1).contiguous() if self.params.get("shared_ff") else None
+        self.w_shared_gate = t("shared.sg").reshape(-1).contiguous() if self.has_shared_gate else None
 
     def forward(self, x, residual, ctx):
         p = self.params
@@ -97,7 +115,8 @@ class RoutedExperts(FeedForward):
         chosen_w = ops.empty((tokens, p["top"]), torch.float32, device)
         shared_gate = ops.empty((tokens,), torch.float32, device) if self.w_shared_gate is not None else None
         ops.moe_route(x, self.router, self.w_shared_gate, dense, chosen, chosen_w, shared_gate, p["top"],
-                      p.get("groups") or 0, p.get("group_keep") or 0, norm=norm)
+                      p.get("groups") or 0, p.get("group_keep") or 0, norm=norm, score=p.get("score", "softmax"),
+                      normalize=p.get("normalize", True))
         F, width = p["expert_ff"], p["hidden_size"]
         if self._sorted_rows(tokens, x):
             self._forward_sorted(x, residual, dense, chosen, chosen_w, shared_gate)
@@ -105,7 +124,7 @@ class RoutedExperts(FeedForward):
         gate_up = ops.empty((tokens, 2 * self.columns), dtype, device)
         ops.linear(x, self.w_gate_up, None, gate_up)
         inner = ops.empty((tokens, self.columns), dtype, device)
-        ops.moe_gate_mul(gate_up, dense, shared_gate, inner, E, F)
+        ops.moe_gate_mul(gate_up, dense, shared_gate, inner, E, F, form=self.form)
         ops.linear(inner, self.w_down, None, residual, accumulate=True)
 
     SORTED_FROM = 128             # tokens of a step from which the rows are sorted by expert
@@ -134,7 +153,7 @@ class RoutedExperts(FeedForward):
         gate_up = ops.empty((rows_cap, 2 * F), dtype, device)
         ops.linear_experts(rows, self.w_gate_up[:E * 2 * F], gate_up, tile_expert, E)
         inner = ops.empty((rows_cap, F), dtype, device)
-        ops.moe_gate_mul_rows(gate_up, row_weight, inner)
+        ops.moe_gate_mul_rows(gate_up, row_weight, inner, form=self.form)
         down = ops.empty((rows_cap, width), torch.float32, device)
         ops.linear_experts(inner, self.w_down[:, :E * F], down, tile_expert, E, along_k=True)
         ops.moe_combine(down, row_of, top, residual)
@@ -143,5 +162,5 @@ class RoutedExperts(FeedForward):
             gate_up_shared = ops.empty((tokens, 2 * shared_ff), dtype, device)
             ops.linear(x, self.w_gate_up[E * 2 * F:], None, gate_up_shared)
             inner_shared = ops.empty((tokens, shared_ff), dtype, device)
-            ops.moe_gate_mul(gate_up_shared, dense, shared_gate, inner_shared, 0, shared_ff)
+            ops.moe_gate_mul(gate_up_shared, dense, shared_gate, inner_shared, 0, shared_ff, form=self.form)
             ops.linear(inner_shared, self.w_down[:, E * F:], None, residual, accumulate=True)
