@@ -303,7 +303,9 @@ def _run_reference(args, ref):
 # ---------------------------------------------------------------------------------------------------------
 # --design NAME: the design's prefill and decode throughput beside the closest other model of equal size, and
 # its kernels alone.  Tefopel stands beside GPT-2; Gozunex (windowed attention over a cached latent, wkv layers,
-# routed experts, several residual streams) beside Tefopel (windowed attention, wkv layers, a dense feed-forward).
+# routed experts, several residual streams) beside Tefopel (windowed attention, wkv layers, a dense feed-forward);
+# Zositar (chunked attention with normed heads and borrowed caches, routed experts with clamped activations and a
+# gated dense feed-forward) beside a Tefopel of attention layers only.
 DESIGN_SIZES = {"w1024": "w1024", "w2048": "w2048"}      # named sizes of config/tefopel.py and config/gozunex.py
 DESIGN_CONTEXT = 2048
 
@@ -328,8 +330,16 @@ def design_arm(args):
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
 
     def configs(name):
-        from pagedserve_b200.config import gozunex, tefopel
+        from pagedserve_b200.config import gozunex, tefopel, zositar
 
+        if args.design == "zositar":
+            # Tefopel of equal size without wkv layers: same width, depth, heads and head size, a window as long as
+            # the chunk, a dense feed-forward as wide as what one token uses of the experts
+            size = zositar.NAMED_CONFIGS["zositar-" + name]
+            like = tefopel.repeating_config(width=size["width"], heads=size["heads"], head_dim=size["head_dim"],
+                                            ff=size["ff"], layers=size["layers"], wkv_heads=size["heads"],
+                                            window=size["chunk"], vocab=size["vocab"], every=size["layers"] + 1)
+            return size, {"zositar": zositar.named_config("zositar-" + name), "tefopel": like}
         if args.design == "gozunex":
             # Tefopel of equal size: same width, depth, heads, window and wkv heads; a head as wide as the cached
             # row's flat + turning parts; a dense feed-forward as wide as what one token uses of the experts
@@ -442,6 +452,47 @@ def design_arm(args):
             run = microbench.time_experts(2048, width, size["experts"], size["top"], size["ff"])
             kernels[f"experts_2048_tokens_{name}"] = {**run, "frac_tensor": run["tflops"] / tensor,
                                                       "dense_frac_tensor": run["dense_tflops"] / tensor}
+    elif args.dtype == "bfloat16" and not args.skip_points and args.design == "zositar":
+        from pagedserve_b200.config import zositar
+
+        hbm, tensor = peaks["hbm_gbs"], peaks["bf16_tflops"]
+        kernels = report["kernels"]
+
+        def of_hbm(run):
+            return {**run, "frac_hbm": run["gbs"] / hbm}
+
+        def of_tensor(run):
+            return {**run, "frac_tensor": run["tflops"] / tensor}
+
+        for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
+            size = zositar.NAMED_CONFIGS["zositar-" + name]
+            H, G, d, width, chunk = size["heads"], size["kv_heads"], size["head_dim"], size["width"], size["chunk"]
+            form = ("clamped_swish", 7.0, 7.0, zositar.EXPERT_SIGMOID_SLOPE)
+            # the same attention kernels with a chunked mask beside a window of the chunk's length (with Tefopel's
+            # score cap and sinks); whole chunks, and chunks that end inside the prompt
+            for batch in (8, 64):
+                kernels[f"decode_attention_b{batch}_{name}"] = {
+                    "tefopel": of_hbm(microbench.time_decode_attention(batch, 1024, H, G, d, window=chunk, softcap=50.0, sink=True)),
+                    "zositar": of_hbm(microbench.time_decode_attention(batch, 1024, H, G, d, chunk=chunk))}
+            kernels[f"decode_attention_b64_quarter_chunks_{name}"] = {
+                "tefopel": of_hbm(microbench.time_decode_attention(64, 1024, H, G, d, window=chunk // 4, softcap=50.0, sink=True)),
+                "zositar": of_hbm(microbench.time_decode_attention(64, 1024, H, G, d, chunk=chunk // 4))}
+            if d in (64, 128):
+                kernels[f"prefill_attention_{name}"] = {
+                    "tefopel": of_tensor(microbench.time_prefill_attention(2, 1024, H, G, d, window=chunk, softcap=50.0, sink=True)),
+                    "zositar": of_tensor(microbench.time_prefill_attention(2, 1024, H, G, d, chunk=chunk))}
+                kernels[f"prefill_attention_quarter_chunks_{name}"] = {
+                    "tefopel": of_tensor(microbench.time_prefill_attention(2, 1024, H, G, d, window=chunk // 4, softcap=50.0, sink=True)),
+                    "zositar": of_tensor(microbench.time_prefill_attention(2, 1024, H, G, d, chunk=chunk // 4))}
+            for label, tokens in (("prefill_2048", 2048), ("decode_b64", 64)):
+                like = microbench.time_cache_write(tokens, H, G, d, rot_dims=(d // 4) * 2)
+                kernels[f"cache_write_{label}_{name}"] = {
+                    "tefopel": {"us": like["us"], "gbs": like["gbs"], "frac_hbm": like["gbs"] / hbm},
+                    "zositar": of_hbm(microbench.time_head_norm_cache_write(tokens, H, G, d, rot_dims=(d // 4) * 2))}
+            like = microbench.time_experts(2048, width, size["experts"], size["top"], size["expert_ff"])
+            own = microbench.time_experts(2048, width, size["experts"], size["top"], size["expert_ff"], score="sigmoid",
+                                          normalize=False, form=form)
+            kernels[f"experts_2048_tokens_{name}"] = {"gozunex": of_tensor(like), "zositar": of_tensor(own)}
     elif args.dtype == "bfloat16" and not args.skip_points:
         hbm, tensor = peaks["hbm_gbs"], peaks["bf16_tflops"]
         kernels = report["kernels"]
@@ -485,7 +536,7 @@ def main():
     parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
                         help="instead of the decode measurement: this many requests (prompts U[64,1024), outputs "
                              "U[32,256]) through the scheduler, chunked prefill under a 2,048-token budget")
-    parser.add_argument("--design", default=None, choices=("tefopel", "gozunex"),
+    parser.add_argument("--design", default=None, choices=("tefopel", "gozunex", "zositar"),
                         help="instead of the default workload: prefill and decode throughput of this design at a few "
                              "sizes beside GPT-2 of equal size, and its kernels alone against the measured peaks")
     parser.add_argument("--design-sizes", default=None, help="comma-separated names out of: " + ", ".join(DESIGN_SIZES))

@@ -234,6 +234,185 @@ head_norm_rotary_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
     }
 }
 
+
+// The same step with four neighbouring numbers per access, for head sizes, strides and addresses that are multiples
+// of four elements.  A head is worked on by `lanes` lanes of a warp (a power of two, at least head_dim / 4 up to 32:
+// with short heads a warp takes several heads at once), each lane holding one or two groups of four numbers; the
+// sum of squares is reduced inside the head's lanes.  Neighbours paired: both numbers of a pair are in one lane.
+// Halves paired: normed numbers pass through shared memory, written and (when a half is a multiple of four) read a
+// quad per access, which keeps the banks free of conflicts; scalar accesses of stride four were what bounded this
+// kernel before.  Every result leaves as one access of four.  Queries, keys and values are separate units of work:
+// a token has n_heads + 2 * n_kv_heads of them (values are copied).  The gains are read by quads too: dim is a
+// multiple of four and the gain tables start on 16-byte boundaries (the launcher checks).
+template <typename T> struct QuadOf;
+template <> struct QuadOf<float> { using type = float4; };
+template <> struct QuadOf<__nv_bfloat16> { using type = uint2; };
+__device__ __forceinline__ void quad_to_float(const float4& v, float (&x)[4]) { x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w; }
+__device__ __forceinline__ void quad_to_float(const uint2& v, float (&x)[4]) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+}
+__device__ __forceinline__ void quad_from_float(const float (&x)[4], float4& v) { v = make_float4(x[0], x[1], x[2], x[3]); }
+__device__ __forceinline__ void quad_from_float(const float (&x)[4], uint2& v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]), b = __floats2bfloat162_rn(x[2], x[3]);
+    v.x = *reinterpret_cast<const uint32_t*>(&a);
+    v.y = *reinterpret_cast<const uint32_t*>(&b);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(HEAD_NORM_WARPS * 32, 16)
+head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                              const T* __restrict__ v, int v_stride, const float* __restrict__ q_gain,
+                              const float* __restrict__ k_gain, float eps, const float2* __restrict__ inv_freq,
+                              int rot_dims, int interleaved, const int* __restrict__ token_row,
+                              const int* __restrict__ positions, const int* __restrict__ block_table, int bt_stride,
+                              T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride, int n_heads,
+                              int n_kv_heads, int head_dim, int dim, int page_size, int lanes) {
+    using Q = typename QuadOf<T>::type;
+    __shared__ __align__(16) float2 turn[ROTARY_MAX_PAIRS];
+    __shared__ __align__(16) float staged[HEAD_NORM_WARPS][HEAD_NORM_MAX_DIM];
+    const int t = blockIdx.x;
+    // positions, rows and the block table are static for the step: read before the wait
+    const int p = positions[t];
+    long long page_base = -1;
+    if (k && k_pool) {
+        const int page = block_table[(size_t)token_row[t] * bt_stride + p / page_size];
+        if (page >= 0) page_base = (long long)page * page_stride + (long long)(p % page_size) * head_dim;
+    }
+    const int half = rot_dims >> 1;
+    const float pos = (float)p;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float2 f = inv_freq[i];
+        const float high = pos * f.x;
+        const float low = fmaf(pos, f.x, -high) + pos * f.y;
+        float sn, cs;
+        sincosf(high, &sn, &cs);
+        turn[i] = make_float2(fmaf(-low, sn, cs), fmaf(low, cs, sn));
+    }
+    pdl_prologue();
+    q = pdl_fresh(q);
+    k = pdl_fresh(k);
+    v = pdl_fresh(v);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_warp = 32 / lanes, group = lane / lanes, gl = lane - group * lanes;
+    const int kv = k ? n_kv_heads : 0;
+    const int total = n_heads + 2 * kv;
+    float* mine = staged[warp] + group * (lanes * 4);       // lanes < 32: a head has at most 4 * lanes numbers
+    const int step = gridDim.y * HEAD_NORM_WARPS * per_warp;
+    for (int base = (blockIdx.y * HEAD_NORM_WARPS + warp) * per_warp; base < total; base += step) {
+        // where this unit of work reads and writes: queries in place, keys and values from their rows into the pages
+        const int unit = base + group;
+        const bool is_query = unit < n_heads, is_value = unit >= n_heads + kv;
+        const T* src = nullptr;
+        T* dst = nullptr;
+        if (unit < total) {
+            if (is_query) {
+                dst = q + (size_t)t * q_stride + (size_t)unit * head_dim;
+                src = dst;
+            } else {
+                const int g = is_value ? unit - n_heads - kv : unit - n_heads;
+                src = (is_value ? v + (size_t)t * v_stride : k + (size_t)t * k_stride) + (size_t)g * head_dim;
+                if (page_base >= 0) dst = (is_value ? v_pool : k_pool) + page_base + (long long)g * page_size * head_dim;
+            }
+        }
+        float x[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int d0 = (gl + j * lanes) * 4;
+            if (dst && d0 < head_dim && (j == 0 || lanes == 32)) {
+                const Q raw = *reinterpret_cast<const Q*>(src + d0);
+                if (is_value) *reinterpret_cast<Q*>(dst + d0) = raw;          // values go straight to their page
+                else quad_to_float(raw, x[j]);
+            }
+        }
+        const bool turns = dst && !is_value;
+        const float* gain = is_query ? q_gain : k_gain;
+        float sq = 0.f;
+        if (turns) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int d0 = (gl + j * lanes) * 4;
+                if (d0 < dim && (j == 0 || lanes == 32)) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sq = fmaf(x[j][e], x[j][e], sq);
+                }
+            }
+        }
+        for (int o = lanes >> 1; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        const float inv = gain ? 1.0f / sqrtf(sq / (float)dim + eps) : 1.0f;
+        if (turns) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int d0 = (gl + j * lanes) * 4;
+                if (d0 < head_dim && (j == 0 || lanes == 32)) {
+                    if (gain && d0 < dim) {
+                        const float4 w = *reinterpret_cast<const float4*>(gain + d0);
+                        x[j][0] = x[j][0] * inv * w.x;
+                        x[j][1] = x[j][1] * inv * w.y;
+                        x[j][2] = x[j][2] * inv * w.z;
+                        x[j][3] = x[j][3] * inv * w.w;
+                    }
+                    // partners in another quad: the normed numbers pass through shared memory, a quad per access
+                    if (!interleaved) *reinterpret_cast<float4*>(mine + d0) = make_float4(x[j][0], x[j][1], x[j][2], x[j][3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (turns) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int d0 = (gl + j * lanes) * 4;
+                if (d0 < head_dim && (j == 0 || lanes == 32)) {
+                    float y[4] = {x[j][0], x[j][1], x[j][2], x[j][3]};
+                    if (d0 < rot_dims) {
+                        if (interleaved) {
+                            // both pairs of the quad are in this lane's registers; rot_dims is even, so a quad
+                            // holds two turning pairs or, at the end, one
+                            const float2 t0 = turn[d0 >> 1];
+                            y[0] = x[j][0] * t0.x - x[j][1] * t0.y;
+                            y[1] = x[j][1] * t0.x + x[j][0] * t0.y;
+                            if (d0 + 2 < rot_dims) {
+                                const float2 t1 = turn[(d0 >> 1) + 1];
+                                y[2] = x[j][2] * t1.x - x[j][3] * t1.y;
+                                y[3] = x[j][3] * t1.x + x[j][2] * t1.y;
+                            }
+                        } else if (!(half & 3)) {
+                            // halves of a multiple of four: the partner quad and its four (cos, sin) in whole accesses
+                            const bool first = d0 < half;
+                            const int pair = first ? d0 : d0 - half;
+                            const float4 o = *reinterpret_cast<const float4*>(mine + (first ? d0 + half : d0 - half));
+                            const float4 ta = *reinterpret_cast<const float4*>(&turn[pair]);
+                            const float4 tb = *reinterpret_cast<const float4*>(&turn[pair + 2]);
+                            const float sign = first ? -1.f : 1.f;
+                            y[0] = fmaf(sign * o.x, ta.y, x[j][0] * ta.x);
+                            y[1] = fmaf(sign * o.y, ta.w, x[j][1] * ta.z);
+                            y[2] = fmaf(sign * o.z, tb.y, x[j][2] * tb.x);
+                            y[3] = fmaf(sign * o.w, tb.w, x[j][3] * tb.z);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int d = d0 + e;
+                                if (d < rot_dims) {
+                                    const bool first = d < half;
+                                    const float2 cs_sn = turn[first ? d : d - half];
+                                    const float o = mine[first ? d + half : d - half];
+                                    y[e] = first ? x[j][e] * cs_sn.x - o * cs_sn.y : x[j][e] * cs_sn.x + o * cs_sn.y;
+                                }
+                            }
+                        }
+                    }
+                    Q packed;
+                    quad_from_float(y, packed);
+                    *reinterpret_cast<Q*>(dst + d0) = packed;
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
 }  // namespace ps
 
 // Heads that are normed, then turned (see head_norm_rotary_kernel).  q [T, n_heads * head_dim] in place; k, v
@@ -255,6 +434,31 @@ PS_EXPORT int ps_head_norm_rotary_cache_write(void* q, int q_stride, const void*
     if (!positions || !q || (k && !v) || (!k && v)) return PS_ERR_BAD_ARGUMENT;
     if (k && k_pool && (!v_pool || !token_row || !block_table || page_size <= 0)) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
+    const int elem = dtype == PS_F32 ? 4 : 2;
+    const uintptr_t addresses = (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)k_pool | (uintptr_t)v_pool;
+    const bool gains_by_quads = !(dim & 3) && !(((uintptr_t)q_gain | (uintptr_t)k_gain) & 15);
+    const bool quads = gains_by_quads && head_dim <= ps::HEAD_NORM_MAX_DIM && !(head_dim & 3) && !(q_stride & 3) && !(k_stride & 3) && !(v_stride & 3) && !(page_stride & 3) &&
+                       !(addresses & (uintptr_t)(4 * elem - 1));
+    if (quads && (dtype == PS_F32 || dtype == PS_BF16)) {
+        int lanes = 1;
+        while (lanes < 32 && lanes * 4 < head_dim) lanes <<= 1;
+        const int units = n_heads + (k ? 2 * n_kv_heads : 0);
+        const int per_cta = ps::HEAD_NORM_WARPS * (32 / lanes);
+        int split = (units + per_cta - 1) / per_cta;
+        if (T >= 2048 && split > 2) split = 2;               // many tokens: fewer CTAs, each walks several heads
+        const dim3 grid(T, split), block(ps::HEAD_NORM_WARPS * 32);
+        if (dtype == PS_F32)
+            return ps::launch_pdl(ps::head_norm_rotary_quads_kernel<float>, grid, block, 0, s, (float*)q, q_stride,
+                                  (const float*)k, k_stride, (const float*)v, v_stride, q_gain, k_gain, eps,
+                                  (const float2*)inv_freq, rot_dims, interleaved, token_row, positions, block_table,
+                                  bt_stride, (float*)k_pool, (float*)v_pool, page_stride, n_heads, n_kv_heads,
+                                  head_dim, dim, page_size, lanes);
+        return ps::launch_pdl(ps::head_norm_rotary_quads_kernel<__nv_bfloat16>, grid, block, 0, s, (__nv_bfloat16*)q,
+                              q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_gain,
+                              k_gain, eps, (const float2*)inv_freq, rot_dims, interleaved, token_row, positions,
+                              block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride,
+                              n_heads, n_kv_heads, head_dim, dim, page_size, lanes);
+    }
     const int heads = n_heads + (k ? n_kv_heads : 0);
     int split = (heads + ps::HEAD_NORM_WARPS - 1) / ps::HEAD_NORM_WARPS;
     if (T >= 2048 && split > 2) split = 2;                   // many tokens: fewer CTAs, each walks several heads

@@ -132,7 +132,7 @@ def _paged_inputs(items, context, kv_heads, head_dim, page, rotate_mb=200, plane
 
 
 def time_decode_attention(batch, context, heads, kv_heads, head_dim, page=16, window=None, softcap=None,
-                          sink=False, iters=20, planes=2):
+                          sink=False, iters=20, planes=2, chunk=None):
     """One decode token per request over ``context`` keys (bfloat16 split-key kernel); GB/s over the K and V
     bytes a token may see (with one plane: over the rows once)."""
     from pagedserve_b200.kernels.ops import Ops
@@ -145,6 +145,8 @@ def time_decode_attention(batch, context, heads, kv_heads, head_dim, page=16, wi
     positions = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     sinks = torch.randn(heads, device="cuda") if sink else None
+    if chunk:                                           # a chunked mask travels as a negative window
+        window = -chunk
 
     def run(i):
         layer = i % layers
@@ -153,13 +155,15 @@ def time_decode_attention(batch, context, heads, kv_heads, head_dim, page=16, wi
                                    status=status, softcap=softcap, sink=sinks)
 
     seconds = _time(run, iters, graph=True)
-    seen = min(context, window) if window else context
+    seen = min(context, window) if window and window > 0 else context
+    if chunk:
+        seen = (context - 1) % chunk + 1
     nbytes = batch * seen * kv_heads * head_dim * 2 * planes
     return {"us": seconds * 1e6, "gbs": nbytes / seconds / 1e9, "status": int(status.item())}
 
 
 def time_prefill_attention(prompts, prompt_len, heads, kv_heads, head_dim, page=16, window=None, softcap=None,
-                           sink=False, iters=10, planes=2):
+                           sink=False, iters=10, planes=2, chunk=None):
     """Whole prompts through the tcgen05 prompt kernel (bfloat16, head size 64 or 128); TFLOP/s over the
     products of the keys a query may see."""
     from pagedserve_b200.kernels.ops import Ops
@@ -174,13 +178,18 @@ def time_prefill_attention(prompts, prompt_len, heads, kv_heads, head_dim, page=
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     sinks = torch.randn(heads, device="cuda") if sink else None
     blocks = prompts * -(-prompt_len // 128)
+    if chunk:
+        window = -chunk
 
     def run(i):
         ops.prefill_attention_tc(q, out, pool, 0, q_start, kv_len, table, 0, prompts, blocks, heads, kv_heads,
                                  head_dim, page, window, head_dim ** -0.5, status=status, softcap=softcap, sink=sinks)
 
     seconds = _time(run, iters, graph=True)
-    if window and window < prompt_len:
+    if chunk:
+        whole, rest = divmod(prompt_len, chunk)
+        pairs = whole * chunk * (chunk + 1) / 2.0 + rest * (rest + 1) / 2.0
+    elif window and window < prompt_len:
         pairs = window * (window + 1) / 2.0 + (prompt_len - window) * float(window)
     else:
         pairs = prompt_len * (prompt_len + 1) / 2.0
@@ -241,6 +250,34 @@ def time_cache_write(tokens, heads, kv_heads, head_dim, page=16, rot_dims=None, 
     moved = tokens * head_dim * 2 * (2 * heads + 3 * kv_heads)
     return {"us": turned * 1e6, "gbs": moved / turned / 1e9, "plain_write_us": plain * 1e6,
             "plain_write_gbs": tokens * head_dim * 2 * 4 * kv_heads / plain / 1e9}
+
+
+def time_head_norm_cache_write(tokens, heads, kv_heads, head_dim, page=16, rot_dims=None, iters=20):
+    """The kernel that norms and turns query and key heads (halves paired) and fills the pages with keys and
+    values; GB/s over queries, keys and values read and written."""
+    from types import SimpleNamespace
+
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    pool, table, _, stride = _paged_inputs(1, tokens, kv_heads, head_dim, page, rotate_mb=0)
+    q = torch.randn(tokens, heads * head_dim, device="cuda").to(torch.bfloat16)
+    k = torch.randn(tokens, kv_heads * head_dim, device="cuda").to(torch.bfloat16)
+    v = torch.randn(tokens, kv_heads * head_dim, device="cuda").to(torch.bfloat16)
+    rot = head_dim if rot_dims is None else rot_dims
+    freq = 10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1))
+    high = freq.float()
+    inv_freq = torch.stack([high, (freq - high.double()).float()], dim=1).contiguous().cuda()
+    gain = torch.ones(head_dim, device="cuda")
+    item = torch.zeros(tokens, dtype=torch.int32, device="cuda")
+    positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    layer = SimpleNamespace(k_pool=pool[:, 0, 0], v_pool=pool[:, 0, 1], page_stride=stride, page_size=page,
+                            block_table=table)
+    ctx = SimpleNamespace(token_slot=item, positions=positions)
+    seconds = _time(lambda i: ops.head_norm_rotary_cache_write(q, k, v, gain, gain, 1e-6, inv_freq, rot, False, head_dim,
+                                                               ctx, layer, heads, kv_heads, head_dim), iters, graph=True)
+    moved = tokens * head_dim * 2 * (2 * heads + 4 * kv_heads)
+    return {"us": seconds * 1e6, "gbs": moved / seconds / 1e9}
 
 
 def time_shared_position_attention(batch, context, heads, head_dim, page=16, window=None, iters=20):
@@ -307,10 +344,12 @@ def time_hyper_step(tokens, width, streams, iters=20):
     return {"us": seconds * 1e6, "gbs": moved / seconds / 1e9}
 
 
-def time_experts(tokens, width, experts, top, ff, iters=10):
+def time_experts(tokens, width, experts, top, ff, iters=10, score="softmax", normalize=True, form=None):
     """The routed part of a feed-forward of ``experts`` experts, rows sorted by expert: router, plan, gather, the
     two tcgen05 products over expert tiles, gate, combine; beside the two plain tcgen05 products of a dense
-    feed-forward with the same inner size per token (top * ff).  TFLOP/s over the useful products."""
+    feed-forward with the same inner size per token (top * ff).  TFLOP/s over the useful products.  ``score``,
+    ``normalize`` and ``form`` as the router and the inner activation take them (sigmoid scores that are the
+    weights; clamped experts)."""
     from pagedserve_b200.kernels.ops import Ops
 
     ops = Ops(torch.bfloat16)
@@ -336,23 +375,23 @@ def time_experts(tokens, width, experts, top, ff, iters=10):
     parts = {}
 
     def routed(i):
-        ops.moe_route(x, router, None, dense, chosen, chosen_w, None, top, 0, 0)
+        ops.moe_route(x, router, None, dense, chosen, chosen_w, None, top, 0, 0, score=score, normalize=normalize)
         ops.moe_plan(chosen, chosen_w, experts, row_of, row_token, row_weight, tile_expert)
         ops.moe_gather(x, row_token, rows)
         ops.linear_experts(rows, w_gu, gate_up, tile_expert, experts)
-        ops.moe_gate_mul_rows(gate_up, row_weight, inner)
+        ops.moe_gate_mul_rows(gate_up, row_weight, inner, form=form)
         ops.linear_experts(inner, w_down, down, tile_expert, experts, along_k=True)
         ops.moe_combine(down, row_of, top, y)
 
     seconds = _time(routed, iters, graph=True)
-    parts["route_us"] = _time(lambda i: ops.moe_route(x, router, None, dense, chosen, chosen_w, None, top, 0, 0), iters,
+    parts["route_us"] = _time(lambda i: ops.moe_route(x, router, None, dense, chosen, chosen_w, None, top, 0, 0, score=score, normalize=normalize), iters,
                               graph=True) * 1e6
     parts["plan_us"] = _time(lambda i: ops.moe_plan(chosen, chosen_w, experts, row_of, row_token, row_weight, tile_expert),
                              iters, graph=True) * 1e6
     parts["gather_us"] = _time(lambda i: ops.moe_gather(x, row_token, rows), iters, graph=True) * 1e6
     parts["gate_up_us"] = _time(lambda i: ops.linear_experts(rows, w_gu, gate_up, tile_expert, experts), iters,
                                 graph=True) * 1e6
-    parts["gate_mul_us"] = _time(lambda i: ops.moe_gate_mul_rows(gate_up, row_weight, inner), iters, graph=True) * 1e6
+    parts["gate_mul_us"] = _time(lambda i: ops.moe_gate_mul_rows(gate_up, row_weight, inner, form=form), iters, graph=True) * 1e6
     parts["down_us"] = _time(lambda i: ops.linear_experts(inner, w_down, down, tile_expert, experts, along_k=True), iters,
                              graph=True) * 1e6
     parts["combine_us"] = _time(lambda i: ops.moe_combine(down, row_of, top, y), iters, graph=True) * 1e6

@@ -646,3 +646,76 @@ def test_a_standing_out_key_among_single_tokens_of_other_requests(dtype, tol):
             engine.cache.free(name)
         assert rel_err(residual, torch.stack([want[name] for name in order])) < tol, (query_at, key_at)
     engine.check_status()
+
+
+# ------------------------------------------------------------------ the kernel that norms, turns and fills the pages
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,kv_heads,slot,dim,rot_dims,interleaved", [
+    (4, 2, 16, 16, 8, False), (16, 16, 64, 64, 32, False), (3, 1, 128, 128, 128, False), (6, 1, 96, 80, 20, False),
+    (5, 5, 32, 20, 6, False), (2, 2, 256, 256, 64, False), (3, 3, 20, 20, 6, False), (6, 2, 24, 10, 0, False),
+    (2, 1, 18, 18, 10, False), (3, 2, 7, 7, 4, False), (4, 4, 48, 48, 16, True), (2, 1, 10, 10, 6, True)])
+def test_heads_are_normed_then_turned_and_cached(dtype, heads, kv_heads, slot, dim, rot_dims, interleaved):
+    """Queries in place, keys into the key pages, values into the value pages, against the plain norm and rotation;
+    heads padded behind ``dim``, sizes with and without a factor of four (two kernels), rows that are column blocks
+    of a wider matrix, a second call that prepares queries only."""
+    from types import SimpleNamespace
+
+    from pagedserve_b200.kernels.ops import Ops
+
+    compute = TORCH_DTYPE[dtype]
+    ops = Ops(compute)
+    g = torch.Generator().manual_seed(heads * 100 + slot)
+    T, page, pages = 37, 8, 12
+    qw, kw = heads * slot, kv_heads * slot
+    projected = torch.randn(T, qw + 2 * kw, generator=g).to(compute)
+    base = 10000.0
+    freq = base ** (-2.0 * torch.arange(rot_dims // 2, dtype=torch.float64) / max(rot_dims, 1))
+    inv_freq = torch.stack([freq.float(), (freq - freq.float().double()).float()], dim=1).contiguous().to(DEV)
+    q_gain, k_gain = 1.0 + 0.2 * torch.randn(dim, generator=g), 1.0 + 0.2 * torch.randn(dim, generator=g)
+    positions = torch.tensor([5 + 3 * t if t < 20 else 700 + t for t in range(T)], dtype=torch.int32)
+    # two requests: tokens 0..19 of slot 1, the rest of slot 0; table rows by slot
+    token_slot = torch.tensor([1] * 20 + [0] * 17, dtype=torch.int32)
+    table = torch.full((2, 128), -1, dtype=torch.int32)
+    order = torch.randperm(pages, generator=g).tolist()
+    need = {(int(s), int(p) // page) for s, p in zip(token_slot, positions)}
+    assert len(need) <= pages
+    for number, (s, index) in enumerate(sorted(need)):
+        table[s, index] = order[number]
+    pool = torch.zeros(pages, 2, kv_heads, page, slot, dtype=compute, device=DEV)
+    layer = SimpleNamespace(k_pool=pool[:, 0], v_pool=pool[:, 1], page_stride=pool.stride(0), page_size=page,
+                            block_table=table.to(DEV))
+    ctx = SimpleNamespace(token_slot=token_slot.to(DEV), positions=positions.to(DEV))
+    device_rows = projected.to(DEV)
+    q, k, v = device_rows[:, :qw], device_rows[:, qw:qw + kw], device_rows[:, qw + kw:]
+    ops.head_norm_rotary_cache_write(q, k, v, q_gain.to(DEV), k_gain.to(DEV), 1e-5, inv_freq, rot_dims, interleaved, dim,
+                                     ctx, layer, heads, kv_heads, slot)
+
+    def plain_heads(rows, count, gain):
+        x = rows.double().reshape(T, count, slot)
+        normed = plain.rms_norm(x[..., :dim], gain.double(), 1e-5)
+        if interleaved:                              # neighbours paired: the halves layout on reordered numbers
+            turning = torch.cat([normed[..., 0:rot_dims:2], normed[..., 1:rot_dims:2]], -1)
+            turned = plain.rotate_halves(turning, positions.long(), rot_dims, base)
+            normed = normed.clone()
+            normed[..., 0:rot_dims:2], normed[..., 1:rot_dims:2] = turned[..., :rot_dims // 2], turned[..., rot_dims // 2:]
+        else:
+            normed = plain.rotate_halves(normed, positions.long(), rot_dims, base)
+        return torch.cat([normed, x[..., dim:]], -1)
+
+    tol = 2e-6 if dtype == "float32" else 1e-2
+    want_q = plain_heads(projected[:, :qw], heads, q_gain)
+    assert rel_err(q.reshape(T, heads, slot), want_q) < tol
+    want_k = plain_heads(projected[:, qw:qw + kw], kv_heads, k_gain)
+    want_v = projected[:, qw + kw:].reshape(T, kv_heads, slot)
+    cached = pool.cpu()
+    for t in range(T):
+        at = cached[int(table[int(token_slot[t]), int(positions[t]) // page]), :, :, int(positions[t]) % page]
+        assert rel_err(at[0], want_k[t]) < tol, t
+        assert torch.equal(at[1], want_v[t]), t
+    assert torch.equal(device_rows[:, qw:].cpu(), projected[:, qw:])                 # keys and values as projected
+    # queries only (a layer that reads another layer's pages): nothing else is touched
+    before = pool.clone()
+    again = projected[:, :qw].to(DEV).contiguous()
+    ops.head_norm_rotary_cache_write(again, None, None, q_gain.to(DEV), None, 1e-5, inv_freq, rot_dims, interleaved, dim,
+                                     ctx, layer, heads, kv_heads, slot)
+    assert rel_err(again.reshape(T, heads, slot), want_q) < tol and torch.equal(pool, before)
