@@ -236,8 +236,9 @@ head_norm_rotary_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
 
 
 // The same step with four neighbouring numbers per access, for head sizes, strides and addresses that are multiples
-// of four elements.  A head is worked on by `lanes` lanes of a warp (a power of two, at least head_dim / 4 up to 32:
-// with short heads a warp takes several heads at once), each lane holding one or two groups of four numbers; the
+// of four elements.  A head is worked on by `lanes` lanes of a warp (a power of two, at least head_dim / 8 up to 32:
+// a warp takes several heads at once unless a head has more than 128 numbers), each lane holding two groups of four
+// numbers, `4 * lanes` apart, whose loads are issued together (twice the bytes in flight of one group a lane); the
 // sum of squares is reduced inside the head's lanes.  Neighbours paired: both numbers of a pair are in one lane.
 // Halves paired: normed numbers pass through shared memory, written and (when a half is a multiple of four) read a
 // quad per access, which keeps the banks free of conflicts; scalar accesses of stride four were what bounded this
@@ -299,7 +300,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
     const int per_warp = 32 / lanes, group = lane / lanes, gl = lane - group * lanes;
     const int kv = k ? n_kv_heads : 0;
     const int total = n_heads + 2 * kv;
-    float* mine = staged[warp] + group * (lanes * 4);       // lanes < 32: a head has at most 4 * lanes numbers
+    float* mine = staged[warp] + group * (lanes * 8);       // a head has at most 8 * lanes numbers
     const int step = gridDim.y * HEAD_NORM_WARPS * per_warp;
     for (int base = (blockIdx.y * HEAD_NORM_WARPS + warp) * per_warp; base < total; base += step) {
         // where this unit of work reads and writes: queries in place, keys and values from their rows into the pages
@@ -321,7 +322,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int d0 = (gl + j * lanes) * 4;
-            if (dst && d0 < head_dim && (j == 0 || lanes == 32)) {
+            if (dst && d0 < head_dim) {
                 const Q raw = *reinterpret_cast<const Q*>(src + d0);
                 if (is_value) *reinterpret_cast<Q*>(dst + d0) = raw;          // values go straight to their page
                 else quad_to_float(raw, x[j]);
@@ -334,7 +335,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int d0 = (gl + j * lanes) * 4;
-                if (d0 < dim && (j == 0 || lanes == 32)) {
+                if (d0 < dim) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) sq = fmaf(x[j][e], x[j][e], sq);
                 }
@@ -346,7 +347,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int d0 = (gl + j * lanes) * 4;
-                if (d0 < head_dim && (j == 0 || lanes == 32)) {
+                if (d0 < head_dim) {
                     if (gain && d0 < dim) {
                         const float4 w = *reinterpret_cast<const float4*>(gain + d0);
                         x[j][0] = x[j][0] * inv * w.x;
@@ -364,7 +365,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int d0 = (gl + j * lanes) * 4;
-                if (d0 < head_dim && (j == 0 || lanes == 32)) {
+                if (d0 < head_dim) {
                     float y[4] = {x[j][0], x[j][1], x[j][2], x[j][3]};
                     if (d0 < rot_dims) {
                         if (interleaved) {
@@ -441,7 +442,7 @@ PS_EXPORT int ps_head_norm_rotary_cache_write(void* q, int q_stride, const void*
                        !(addresses & (uintptr_t)(4 * elem - 1));
     if (quads && (dtype == PS_F32 || dtype == PS_BF16)) {
         int lanes = 1;
-        while (lanes < 32 && lanes * 4 < head_dim) lanes <<= 1;
+        while (lanes < 32 && lanes * 8 < head_dim) lanes <<= 1;    // two quads a lane: both loads in flight at once
         const int units = n_heads + (k ? 2 * n_kv_heads : 0);
         const int per_cta = ps::HEAD_NORM_WARPS * (32 / lanes);
         int split = (units + per_cta - 1) / per_cta;
