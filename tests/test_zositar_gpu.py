@@ -66,7 +66,27 @@ CONFIG_F = plain.make_config(
 # a chunk longer than any prompt of these tests: every earlier key is seen, hundreds of tokens back
 CONFIG_G = plain.make_config([A(4, 2, 32, 32, chunk=1000, rot_dims=16, scale=0.18, mlp=None),
                               A(4, 2, 32, 32, chunk=400, rot_dims=16, scale=0.18, mlp=D(32), kv_from=0)], width=56, vocab=67)
-CONFIGS = {"a": (CONFIG_A, 1, 16), "b": (CONFIG_B, 2, 16), "c": (CONFIG_C, 3, 8), "d": (CONFIG_D, 4, 32),   # config, seed, page
+# layers as wide as a small model's (the tensor-core products and prompt attention run at these sizes): sixteen
+# query heads on one key head of 96, heads of 80, a lender with two borrowers that lie apart, a borrower of a
+# borrower's neighbour; and the same with every expert chosen, for bfloat16
+def _middle(top):
+    return plain.make_config(
+        [A(8, 2, 80, 80, chunk=100, rot_dims=40, base=20000.0, scale=0.11, mlp=X(16, top or 2, 64, shared_ff=128)),
+         A(8, 2, 80, 80, chunk=100, rot_dims=40, base=20000.0, scale=0.11, mlp=X(16, top or 2, 64, shared_ff=128), kv_from=0),
+         A(8, 8, 64, 64, chunk=256, rot_dims=16, base=20000.0, scale=0.125, mlp=D(768)),
+         A(8, 2, 80, 80, chunk=100, rot_dims=40, base=20000.0, scale=0.11, mlp=D(256), kv_from=0),
+         A(8, 8, 64, 64, chunk=256, rot_dims=16, base=20000.0, scale=0.125,
+           mlp=X(6, top or 2, 100, limit=2.5, shared_ff=200, shared_limit=2.0), kv_from=2),
+         A(16, 1, 96, 96, chunk=32, rot_dims=96, base=500000.0, scale=0.08,
+           mlp=X(6, top or 1, 100, limit=2.5, shared_ff=200, shared_limit=2.0))],
+        width=512, vocab=700, eps=1e-6)
+
+
+CONFIG_M, CONFIG_N = _middle(None), _middle(6)
+for _layer in CONFIG_N["layers"]:
+    if _layer["mlp"]["kind"] == "moe":
+        _layer["mlp"]["router"]["top"] = _layer["mlp"]["router"]["experts"]
+CONFIGS = {"m": (CONFIG_M, 21, 16), "n": (CONFIG_N, 22, 16), "a": (CONFIG_A, 1, 16), "b": (CONFIG_B, 2, 16), "c": (CONFIG_C, 3, 8), "d": (CONFIG_D, 4, 32),   # config, seed, page
            "e": (CONFIG_E, 5, 16), "f": (CONFIG_F, 6, 8),
            # the same shapes with query gains three times as large: one key can stand out among hundreds
            "sa": (CONFIG_A, 11, 16), "sb": (CONFIG_B, 12, 16), "sc": (CONFIG_C, 13, 8), "sd": (CONFIG_D, 14, 32),
@@ -221,6 +241,15 @@ def test_small_models_of_other_shapes(which, dtype):
     sequences = sequences_for(which, [70, 3, 131, 29, 64, 1], seed=70)
     check_replay(which, dtype, helpers.trace_whole(sequences), sequences, "whole")
     steps = helpers.trace_mixed(sequences, seed=5, live=4, decode_tail=16, max_portion=30)
+    check_replay(which, dtype, steps, sequences, "mixed")
+
+
+@pytest.mark.parametrize("dtype,which", [("float32", "m"), ("bfloat16", "n")])
+def test_a_model_of_middle_size(dtype, which):
+    """A thousand tokens whole, then unequal requests mixed, at layer sizes where the tensor-core kernels run."""
+    sequences = sequences_for(which, [1000, 260, 97, 23, 1], seed=60)
+    check_replay(which, dtype, helpers.trace_whole(sequences), sequences, "whole")
+    steps = helpers.trace_mixed(sequences, seed=6, live=4, decode_tail=24, max_portion=70)
     check_replay(which, dtype, steps, sequences, "mixed")
 
 
