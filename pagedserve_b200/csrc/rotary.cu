@@ -261,16 +261,19 @@ __device__ __forceinline__ void quad_from_float(const float (&x)[4], uint2& v) {
     v.y = *reinterpret_cast<const uint32_t*>(&b);
 }
 
-template <typename T>
+// PAIRING is a template parameter so that a pass carries the code of its own form only: 0 neighbours paired, 1 halves
+// paired with a half that is a multiple of four, 2 halves paired with any even number of turning dimensions.
+template <typename T, int PAIRING>
 __global__ void __launch_bounds__(HEAD_NORM_WARPS * 32, 16)
 head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
                               const T* __restrict__ v, int v_stride, const float* __restrict__ q_gain,
                               const float* __restrict__ k_gain, float eps, const float2* __restrict__ inv_freq,
-                              int rot_dims, int interleaved, const int* __restrict__ token_row,
+                              int rot_dims, const int* __restrict__ token_row,
                               const int* __restrict__ positions, const int* __restrict__ block_table, int bt_stride,
                               T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride, int n_heads,
                               int n_kv_heads, int head_dim, int dim, int page_size, int lanes) {
     using Q = typename QuadOf<T>::type;
+    constexpr bool interleaved = PAIRING == 0;
     __shared__ __align__(16) float2 turn[ROTARY_MAX_PAIRS];
     __shared__ __align__(16) float staged[HEAD_NORM_WARPS][HEAD_NORM_MAX_DIM];
     const int t = blockIdx.x;
@@ -356,7 +359,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
                         x[j][3] = x[j][3] * inv * w.w;
                     }
                     // partners in another quad: the normed numbers pass through shared memory, a quad per access
-                    if (!interleaved) *reinterpret_cast<float4*>(mine + d0) = make_float4(x[j][0], x[j][1], x[j][2], x[j][3]);
+                    if constexpr (!interleaved) *reinterpret_cast<float4*>(mine + d0) = make_float4(x[j][0], x[j][1], x[j][2], x[j][3]);
                 }
             }
         }
@@ -368,7 +371,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
                 if (d0 < head_dim) {
                     float y[4] = {x[j][0], x[j][1], x[j][2], x[j][3]};
                     if (d0 < rot_dims) {
-                        if (interleaved) {
+                        if constexpr (interleaved) {
                             // both pairs of the quad are in this lane's registers; rot_dims is even, so a quad
                             // holds two turning pairs or, at the end, one
                             const float2 t0 = turn[d0 >> 1];
@@ -379,7 +382,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
                                 y[2] = x[j][2] * t1.x - x[j][3] * t1.y;
                                 y[3] = x[j][3] * t1.x + x[j][2] * t1.y;
                             }
-                        } else if (!(half & 3)) {
+                        } else if constexpr (PAIRING == 1) {
                             // halves of a multiple of four: the partner quad and its four (cos, sin) in whole accesses
                             const bool first = d0 < half;
                             const int pair = first ? d0 : d0 - half;
@@ -448,17 +451,18 @@ PS_EXPORT int ps_head_norm_rotary_cache_write(void* q, int q_stride, const void*
         int split = (units + per_cta - 1) / per_cta;
         if (T >= 2048 && split > 2) split = 2;               // many tokens: fewer CTAs, each walks several heads
         const dim3 grid(T, split), block(ps::HEAD_NORM_WARPS * 32);
+        const int pairing = interleaved ? 0 : (((rot_dims >> 1) & 3) ? 2 : 1);
+#define PS_HEAD_NORM_QUADS(TYPE, PAIRING)                                                                              \
+    ps::launch_pdl(ps::head_norm_rotary_quads_kernel<TYPE, PAIRING>, grid, block, 0, s, (TYPE*)q, q_stride,             \
+                   (const TYPE*)k, k_stride, (const TYPE*)v, v_stride, q_gain, k_gain, eps, (const float2*)inv_freq,   \
+                   rot_dims, token_row, positions, block_table, bt_stride, (TYPE*)k_pool, (TYPE*)v_pool, page_stride,  \
+                   n_heads, n_kv_heads, head_dim, dim, page_size, lanes)
         if (dtype == PS_F32)
-            return ps::launch_pdl(ps::head_norm_rotary_quads_kernel<float>, grid, block, 0, s, (float*)q, q_stride,
-                                  (const float*)k, k_stride, (const float*)v, v_stride, q_gain, k_gain, eps,
-                                  (const float2*)inv_freq, rot_dims, interleaved, token_row, positions, block_table,
-                                  bt_stride, (float*)k_pool, (float*)v_pool, page_stride, n_heads, n_kv_heads,
-                                  head_dim, dim, page_size, lanes);
-        return ps::launch_pdl(ps::head_norm_rotary_quads_kernel<__nv_bfloat16>, grid, block, 0, s, (__nv_bfloat16*)q,
-                              q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_gain,
-                              k_gain, eps, (const float2*)inv_freq, rot_dims, interleaved, token_row, positions,
-                              block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride,
-                              n_heads, n_kv_heads, head_dim, dim, page_size, lanes);
+            return pairing == 0 ? PS_HEAD_NORM_QUADS(float, 0)
+                                : pairing == 1 ? PS_HEAD_NORM_QUADS(float, 1) : PS_HEAD_NORM_QUADS(float, 2);
+        return pairing == 0 ? PS_HEAD_NORM_QUADS(__nv_bfloat16, 0)
+                            : pairing == 1 ? PS_HEAD_NORM_QUADS(__nv_bfloat16, 1) : PS_HEAD_NORM_QUADS(__nv_bfloat16, 2);
+#undef PS_HEAD_NORM_QUADS
     }
     const int heads = n_heads + (k ? n_kv_heads : 0);
     int split = (heads + ps::HEAD_NORM_WARPS - 1) / ps::HEAD_NORM_WARPS;
