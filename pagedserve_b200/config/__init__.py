@@ -13,3 +13,4 @@ from pagedserve_b200.config.engine_config import EngineConfig  # noqa: F401
 from pagedserve_b200.config.gpt2 import GPT2Config  # noqa: F401
 from pagedserve_b200.config.tefopel import TefopelConfig  # noqa: F401
 from pagedserve_b200.config.zositar import ZositarConfig  # noqa: F401
+from pagedserve_b200.config.pagatar import PagatarConfig  # noqa: F401

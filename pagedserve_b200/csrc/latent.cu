@@ -15,7 +15,8 @@
 // queries.  Pairs are neighbours (2i, 2i + 1), i < rot_dims / 2, angle p * inv_freq[i]; the other r - rot_dims
 // numbers pass.
 //
-// sigmoid_gate: heads[t, j] *= 1 / (1 + exp(-g[t, j])) in float32.
+// sigmoid_gate: heads[t, j] *= 1 / (1 + exp(-g[t, j / span])) in float32 (span 1: a gate per number; span = a head's
+// size: one gate per head).
 #include "common.cuh"
 
 namespace ps {
@@ -105,7 +106,7 @@ latent_prepare_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
 template <typename T>
 __global__ void __launch_bounds__(256)
 sigmoid_gate_kernel(T* __restrict__ heads, int heads_stride, const T* __restrict__ g, int g_stride, int rows,
-                    int width) {
+                    int width, int span) {
     pdl_prologue();
     heads = pdl_fresh(heads);
     g = pdl_fresh(g);
@@ -114,7 +115,7 @@ sigmoid_gate_kernel(T* __restrict__ heads, int heads_stride, const T* __restrict
          i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / width), c = (int)(i - (long long)r * width);
         T* at = heads + (size_t)r * heads_stride + c;
-        const float z = to_float(g[(size_t)r * g_stride + c]);
+        const float z = to_float(g[(size_t)r * g_stride + c / span]);
         *at = from_float<T>(to_float(*at) / (1.0f + expf(-z)));
     }
 }
@@ -153,20 +154,20 @@ PS_EXPORT int ps_latent_prepare(const void* q, int q_stride, const void* down, i
     return PS_ERR_UNSUPPORTED;
 }
 
-// heads [rows, width] (in place), g [rows, width]: row views of the compute type.
+// heads [rows, width] (in place), g [rows, width / span]: row views of the compute type.
 PS_EXPORT int ps_sigmoid_gate(void* heads, int heads_stride, const void* g, int g_stride, int rows, int width,
-                              int dtype, void* stream) {
+                              int span, int dtype, void* stream) {
     if (rows <= 0 || width <= 0) return PS_OK;
-    if (!heads || !g) return PS_ERR_BAD_ARGUMENT;
+    if (!heads || !g || span <= 0) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const long long total = (long long)rows * width;
     const long long blocks = (total + 255) / 256;
     const dim3 grid((unsigned)(blocks < 2368 ? blocks : 2368));
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::sigmoid_gate_kernel<float>, grid, dim3(256), 0, s, (float*)heads, heads_stride,
-                              (const float*)g, g_stride, rows, width);
+                              (const float*)g, g_stride, rows, width, span);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::sigmoid_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (__nv_bfloat16*)heads,
-                              heads_stride, (const __nv_bfloat16*)g, g_stride, rows, width);
+                              heads_stride, (const __nv_bfloat16*)g, g_stride, rows, width, span);
     return PS_ERR_UNSUPPORTED;
 }

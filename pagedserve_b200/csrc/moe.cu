@@ -80,7 +80,8 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
                  const T* __restrict__ shared_gate_w, float* __restrict__ dense, int* __restrict__ chosen,
                  float* __restrict__ chosen_w, float* __restrict__ shared_gate, int tokens, int W, int E, int top,
                  int groups, int keep, int by8, const float* __restrict__ raw, int raw_stride,
-                 const float* __restrict__ gain, float eps, T* __restrict__ x_out, int score_kind, int normalize) {
+                 const float* __restrict__ gain, float eps, T* __restrict__ x_out, int score_kind, int normalize,
+                 const float* __restrict__ correction) {
     pdl_prologue();
     x = pdl_fresh(x);
     raw = pdl_fresh(raw);
@@ -211,6 +212,8 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
         if (e < E) {
             score[e] = mine[i];
             dense[(size_t)t * E + e] = 0.f;
+            // a correction moves the election only: an expert stands with score + correction, its weight stays the score
+            if (correction) mine[i] += correction[e];
         }
     }
     __syncwarp();
@@ -275,9 +278,9 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
             if (best_e == lane + 32 * i) mine[i] = -INFINITY;
         if (lane == 0) {
             winner[k] = best_e;                                  // -1: fewer open experts than `top`
-            winner_score[k] = best_e >= 0 ? best : 0.f;
+            winner_score[k] = best_e >= 0 ? (correction ? score[best_e] : best) : 0.f;
         }
-        if (best_e >= 0) total += best;
+        if (best_e >= 0) total += correction ? score[best_e] : best;
     }
     __syncwarp();
     const float scale = normalize ? 1.0f / (total + 1e-20f) : 1.0f;
@@ -495,11 +498,13 @@ moe_combine_kernel(const float* __restrict__ down, int down_stride, const int* _
 // x [T, W] rows of the compute type; router [E, W]; shared_gate_w [W] or null; dense float32 [T, E];
 // chosen int32 [T, top]; chosen_w float32 [T, top]; shared_gate float32 [T] (written only with shared_gate_w).
 // raw (may be null): float32 [T, W] rows whose RMS norm (gain float32 [W], eps) is what the router reads: the normed
-// rows are then written to x (which the experts' products read) instead of being read from it.
+// rows are then written to x (which the experts' products read) instead of being read from it.  correction (may be
+// null): float32 [E] added to the scores for the election only.
 PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int router_stride,
                            const void* shared_gate_w, float* dense, int* chosen, float* chosen_w, float* shared_gate,
                            int T, int W, int E, int top, int groups, int keep, int dtype, const float* raw,
-                           int raw_stride, const float* gain, float eps, int score_kind, int normalize, void* stream) {
+                           int raw_stride, const float* gain, float eps, int score_kind, int normalize,
+                           const float* correction, void* stream) {
     if (T <= 0) return PS_OK;
     if (raw && !gain) return PS_ERR_BAD_ARGUMENT;
     if (W <= 0 || E <= 0 || top <= 0 || top > E || !x || !router || !dense || !chosen || !chosen_w)
@@ -518,13 +523,13 @@ PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int 
         return ps::launch_pdl(ps::moe_route_kernel<float>, grid, block, 0, s, (const float*)x, x_stride,
                               (const float*)router, router_stride, (const float*)shared_gate_w, dense, chosen,
                               chosen_w, shared_gate, T, W, E, top, groups, keep, by8, raw, raw_stride, gain, eps,
-                              (float*)const_cast<void*>(x), score_kind, normalize);
+                              (float*)const_cast<void*>(x), score_kind, normalize, correction);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_route_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)x,
                               x_stride, (const __nv_bfloat16*)router, router_stride,
                               (const __nv_bfloat16*)shared_gate_w, dense, chosen, chosen_w, shared_gate, T, W, E, top,
                               groups, keep, by8, raw, raw_stride, gain, eps, (__nv_bfloat16*)const_cast<void*>(x),
-                              score_kind, normalize);
+                              score_kind, normalize, correction);
     return PS_ERR_UNSUPPORTED;
 }
 

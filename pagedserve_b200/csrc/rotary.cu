@@ -163,7 +163,7 @@ head_norm_rotary_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
                         int interleaved, const int* __restrict__ token_row, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pool,
                         T* __restrict__ v_pool, long long page_stride, int n_heads, int n_kv_heads, int head_dim,
-                        int dim, int page_size) {
+                        int dim, int page_size, float amplitude) {
     __shared__ float2 turn[ROTARY_MAX_PAIRS];
     __shared__ float staged[HEAD_NORM_WARPS][HEAD_NORM_MAX_DIM];
     const int t = blockIdx.x;
@@ -176,7 +176,7 @@ head_norm_rotary_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k
         const float low = fmaf(pos, f.x, -high) + pos * f.y;
         float sn, cs;
         sincosf(high, &sn, &cs);
-        turn[i] = make_float2(fmaf(-low, sn, cs), fmaf(low, cs, sn));
+        turn[i] = make_float2(fmaf(-low, sn, cs) * amplitude, fmaf(low, cs, sn) * amplitude);
     }
     pdl_prologue();
     q = pdl_fresh(q);
@@ -271,7 +271,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
                               int rot_dims, const int* __restrict__ token_row,
                               const int* __restrict__ positions, const int* __restrict__ block_table, int bt_stride,
                               T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride, int n_heads,
-                              int n_kv_heads, int head_dim, int dim, int page_size, int lanes) {
+                              int n_kv_heads, int head_dim, int dim, int page_size, int lanes, float amplitude) {
     using Q = typename QuadOf<T>::type;
     constexpr bool interleaved = PAIRING == 0;
     __shared__ __align__(16) float2 turn[ROTARY_MAX_PAIRS];
@@ -292,7 +292,7 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
         const float low = fmaf(pos, f.x, -high) + pos * f.y;
         float sn, cs;
         sincosf(high, &sn, &cs);
-        turn[i] = make_float2(fmaf(-low, sn, cs), fmaf(low, cs, sn));
+        turn[i] = make_float2(fmaf(-low, sn, cs) * amplitude, fmaf(low, cs, sn) * amplitude);
     }
     pdl_prologue();
     q = pdl_fresh(q);
@@ -421,14 +421,15 @@ head_norm_rotary_quads_kernel(T* __restrict__ q, int q_stride, const T* __restri
 
 // Heads that are normed, then turned (see head_norm_rotary_kernel).  q [T, n_heads * head_dim] in place; k, v
 // [T, n_kv_heads * head_dim] or both null (queries only); q_gain / k_gain float32 [dim] or null; inv_freq float32
-// [rot_dims / 2][2] as (high, low) parts; k_pool null: nothing is written to pages.
+// [rot_dims / 2][2] as (high, low) parts; k_pool null: nothing is written to pages.  `amplitude` multiplies every sine
+// and cosine (1: a plain turn).
 PS_EXPORT int ps_head_norm_rotary_cache_write(void* q, int q_stride, const void* k, int k_stride, const void* v,
                                               int v_stride, const float* q_gain, const float* k_gain, float eps,
                                               const float* inv_freq, int rot_dims, int interleaved,
                                               const int* token_row, const int* positions, const int* block_table,
                                               int bt_stride, void* k_pool, void* v_pool, long long page_stride, int T,
                                               int n_heads, int n_kv_heads, int head_dim, int dim, int page_size,
-                                              int dtype, void* stream) {
+                                              int dtype, float amplitude, void* stream) {
     if (T <= 0) return PS_OK;
     if (n_heads <= 0 || n_kv_heads < 0 || head_dim <= 0 || dim <= 0 || dim > head_dim || rot_dims < 0 ||
         rot_dims > dim || (rot_dims & 1))
@@ -456,7 +457,7 @@ PS_EXPORT int ps_head_norm_rotary_cache_write(void* q, int q_stride, const void*
     ps::launch_pdl(ps::head_norm_rotary_quads_kernel<TYPE, PAIRING>, grid, block, 0, s, (TYPE*)q, q_stride,             \
                    (const TYPE*)k, k_stride, (const TYPE*)v, v_stride, q_gain, k_gain, eps, (const float2*)inv_freq,   \
                    rot_dims, token_row, positions, block_table, bt_stride, (TYPE*)k_pool, (TYPE*)v_pool, page_stride,  \
-                   n_heads, n_kv_heads, head_dim, dim, page_size, lanes)
+                   n_heads, n_kv_heads, head_dim, dim, page_size, lanes, amplitude)
         if (dtype == PS_F32)
             return pairing == 0 ? PS_HEAD_NORM_QUADS(float, 0)
                                 : pairing == 1 ? PS_HEAD_NORM_QUADS(float, 1) : PS_HEAD_NORM_QUADS(float, 2);
@@ -473,13 +474,13 @@ PS_EXPORT int ps_head_norm_rotary_cache_write(void* q, int q_stride, const void*
                               (const float*)k, k_stride, (const float*)v, v_stride, q_gain, k_gain, eps,
                               (const float2*)inv_freq, rot_dims, interleaved, token_row, positions, block_table,
                               bt_stride, (float*)k_pool, (float*)v_pool, page_stride, n_heads, n_kv_heads, head_dim,
-                              dim, page_size);
+                              dim, page_size, amplitude);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::head_norm_rotary_kernel<__nv_bfloat16>, grid, block, 0, s, (__nv_bfloat16*)q,
                               q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_gain,
                               k_gain, eps, (const float2*)inv_freq, rot_dims, interleaved, token_row, positions,
                               block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride,
-                              n_heads, n_kv_heads, head_dim, dim, page_size);
+                              n_heads, n_kv_heads, head_dim, dim, page_size, amplitude);
     return PS_ERR_UNSUPPORTED;
 }
 

@@ -33,7 +33,8 @@ NVCC_FLAGS = [
 # library name -> sources (relative to csrc/)
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["embed_norm.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu", "host_io.cu", "step_state.cu", "step_build.cu",
-             "rotary.cu", "wkv.cu", "embed_pair.cu", "hyper.cu", "latent.cu", "moe.cu"],
+             "rotary.cu", "wkv.cu", "embed_pair.cu", "hyper.cu", "latent.cu", "moe.cu", "post_norm.cu", "mingru.cu",
+             "short_conv.cu"],
     "bf16": ["gemm_skinny.cu", "attention_decode.cu", "attention_prefill.cu"],
     "tc": ["gemm_tc.cu", "gemm_rows_tc.cu", "attention_prefill_tc.cu"],
 }

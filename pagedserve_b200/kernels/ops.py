@@ -90,11 +90,17 @@ _SIGNATURES = {
         "ps_hyper_step": [_P, _P, _P, _P, _P, _P, _L, _I, _P],
         "ps_latent_prepare": [_P, _I, _P, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _L, _I, _P, _I, _I, _I, _I, _I, _I,
                               _I, _P],
-        "ps_sigmoid_gate": [_P, _I, _P, _I, _I, _I, _I, _P],
-        "ps_moe_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _F, _I, _I, _P],
+        "ps_sigmoid_gate": [_P, _I, _P, _I, _I, _I, _I, _I, _P],
+        "ps_moe_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _F, _I, _I, _P, _P],
         "ps_moe_gate_mul": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P],
         "ps_head_norm_rotary_cache_write": [_P, _I, _P, _I, _P, _I, _P, _P, _F, _P, _I, _I, _P, _P, _P, _I, _P, _P, _L,
-                                            _I, _I, _I, _I, _I, _I, _I, _P],
+                                            _I, _I, _I, _I, _I, _I, _I, _F, _P],
+        "ps_group_rms_norm": [_P, _L, _I, _P, _I, _I, _I, _P, _F, _P, _L, _I, _P],
+        "ps_post_norm_add": [_P, _P, _I, _I, _I, _P, _F, _P, _I, _P, _L, _I, _P, _P],
+        "ps_depth_begin": [_P, _P, _P, _I, _P, _L, _P],
+        "ps_mingru_scan": [_P, _L, _I, _P, _L, _P, _P, _I, _P, _L, _I, _I, _P],
+        "ps_short_conv": [_P, _L, _P, _I, _I, _I, _P, _L, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P],
+        "ps_short_conv_keep": [_P, _L, _I, _I, _P, _L, _P, _P, _I, _P],
         "ps_moe_plan": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P],
         "ps_moe_gather": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
         "ps_moe_gate_mul_rows": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
@@ -842,13 +848,14 @@ class Ops:
             layer.page_size if pools else 1, self.code, _stream()), "rotary_cache_write")
 
     def head_norm_rotary_cache_write(self, q, k, v, q_gain, k_gain, eps, inv_freq, rot_dims, interleaved, dim, ctx,
-                                     layer, n_heads, n_kv_heads, head_dim, write_cache=True):
+                                     layer, n_heads, n_kv_heads, head_dim, write_cache=True, amplitude=1.0):
         """As :meth:`rotary_cache_write` for heads that are normed before they turn: per head, its first ``dim``
         numbers (of ``head_dim``; the rest is padding) are divided by their root mean square (eps inside the root)
         and multiplied by ``q_gain`` / ``k_gain`` (float32 [dim], one for all heads of a kind; None: no norm), then
         the first ``rot_dims`` turn.  Queries in place, keys into the key pages, the rows of ``v`` into the value
         pages.  ``k`` and ``v`` None: a layer that reads another layer's cache prepares its queries only.
-        ``inv_freq``: float32 [rot_dims / 2, 2] as (high, low) parts (``RotaryPositions.inv_freq_split``)."""
+        ``inv_freq``: float32 [rot_dims / 2, 2] as (high, low) parts (``RotaryPositions.inv_freq_split``);
+        ``amplitude`` multiplies every sine and cosine (a rotation stretched to longer contexts has one above 1)."""
         T = q.shape[0]
         _require(q, "q", self.dtype)
         if (k is None) != (v is None):
@@ -881,7 +888,7 @@ class Ops:
             _ptr(layer.block_table) if pools else None, layer.block_table.stride(0) if pools else 0,
             _ptr(layer.k_pool) if pools else None, _ptr(layer.v_pool) if pools else None,
             layer.page_stride if pools else 0, T, n_heads, n_kv_heads, head_dim, dim,
-            layer.page_size if pools else 1, self.code, _stream()), "head_norm_rotary_cache_write")
+            layer.page_size if pools else 1, self.code, float(amplitude), _stream()), "head_norm_rotary_cache_write")
 
     # ------------------------------------------------------------------ linear recurrence with decay ("wkv")
     def token_shift_mix(self, x, mu, state, prev_offset, ctx, out):
@@ -1047,20 +1054,155 @@ class Ops:
             layer.page_stride if pools else 0, layer.page_size if pools else 1, _ptr(q_out), q_out.stride(0), T,
             n_heads, flat, turning, rank, self.code, _stream()), "latent_prepare")
 
-    def sigmoid_gate(self, heads, g):
-        """heads *= sigmoid(g), elementwise in float32; both [rows, width] row views of the compute type."""
+    def sigmoid_gate(self, heads, g, span=1):
+        """heads[:, j] *= sigmoid(g[:, j // span]) in float32; ``heads`` [rows, width] and ``g`` [rows, width / span]
+        are row views of the compute type (span 1: a gate per number; a head's size: one gate per head)."""
         _require(heads, "heads", self.dtype)
         _require(g, "g", self.dtype)
-        if heads.shape != g.shape or heads.stride(1) != 1 or g.stride(1) != 1:
+        if (heads.shape[0] != g.shape[0] or heads.shape[1] != g.shape[1] * span or heads.stride(1) != 1
+                or g.stride(1) != 1):
             raise KernelError("sigmoid_gate: shapes do not match")
         self.launches += 1
         _check(self.core.ps_sigmoid_gate(_ptr(heads), heads.stride(0), _ptr(g), g.stride(0), heads.shape[0],
-                                         heads.shape[1], self.code, _stream()), "sigmoid_gate")
+                                         heads.shape[1], int(span), self.code, _stream()), "sigmoid_gate")
         return heads
+
+    # ------------------------------------------------------------------ norms in groups, sums behind a norm
+    def group_rms_norm(self, x, gain, eps, groups, out, rows=None):
+        """out[r] = x[rows[r]] (or x[r]) with each of its ``groups`` equal runs divided by the run's root mean square
+        (eps inside the root), times ``gain`` (float32 [H]); csrc/post_norm.cu.  ``x`` rows of float32 or the compute
+        type, ``out`` rows of either; a row may be normed in place."""
+        _require(x, "x")
+        _require(out, "out")
+        _require(gain, "gain", torch.float32)
+        H = x.shape[-1]
+        n_rows = out.shape[0]
+        if rows is not None:
+            _require(rows, "rows", torch.int32)
+            if rows.numel() != n_rows:
+                raise KernelError("group_rms_norm: rows and out disagree")
+        elif x.shape[0] != n_rows:
+            raise KernelError("group_rms_norm: x and out disagree")
+        if (out.shape[-1] != H or gain.numel() != H or x.stride(-1) != 1 or out.stride(-1) != 1 or groups <= 0
+                or H % groups or not gain.is_contiguous()):
+            raise KernelError("group_rms_norm: widths disagree")
+        self.launches += 1
+        _check(self.core.ps_group_rms_norm(_ptr(x), x.stride(0), dtype_code(x.dtype), _ptr(rows), n_rows, H, int(groups),
+                                           _ptr(gain), float(eps), _ptr(out), out.stride(0), dtype_code(out.dtype),
+                                           _stream()), "group_rms_norm")
+        return out
+
+    def post_norm_add(self, y, x, gain, eps, groups, x_cast=None, history=None, n_history=0, weight=None):
+        """x += group_rms_norm(y) * gain, y = 0 (all float32 [T, H]); with ``history`` [n, T, H] the sum is stored as
+        entry ``n_history - 1`` and x becomes sum_j weight[j] * history[j] over the first ``n_history`` entries;
+        ``x_cast`` (compute type) receives a copy of the new x."""
+        for name, tensor in (("y", y), ("x", x)):
+            _require(tensor, name, torch.float32)
+        _require(gain, "gain", torch.float32)
+        T, H = x.shape
+        if y.shape != x.shape or not (x.is_contiguous() and y.is_contiguous()) or gain.numel() != H or H % groups:
+            raise KernelError("post_norm_add: shapes do not match")
+        if x_cast is not None and (x_cast.shape != x.shape or not x_cast.is_contiguous()):
+            raise KernelError("post_norm_add: the copy must have the rows' shape")
+        stride = 0
+        if history is not None:
+            _require(history, "history", torch.float32)
+            _require(weight, "weight", torch.float32)
+            if (history.shape[1:] != x.shape or not history.is_contiguous() or not (0 < n_history <= history.shape[0])
+                    or weight.numel() != n_history or not weight.is_contiguous()):
+                raise KernelError("post_norm_add: the history does not fit")
+            stride = history.stride(0)
+        self.launches += 1
+        _check(self.core.ps_post_norm_add(_ptr(y), _ptr(x), T, H, int(groups), _ptr(gain), float(eps), _ptr(x_cast),
+                                          dtype_code(x_cast.dtype) if x_cast is not None else PS_F32, _ptr(history),
+                                          stride, int(n_history), _ptr(weight), _stream()), "post_norm_add")
+
+    def depth_begin(self, x, first, x_cast, y):
+        """first = x (if given), x_cast = x in the compute type (if given), y = 0; float32 rows of one shape."""
+        _require(x, "x", torch.float32)
+        _require(y, "y", torch.float32)
+        if y.shape != x.shape or not (x.is_contiguous() and y.is_contiguous()):
+            raise KernelError("depth_begin: shapes do not match")
+        for tensor in (first, x_cast):
+            if tensor is not None and (tensor.shape != x.shape or not tensor.is_contiguous()):
+                raise KernelError("depth_begin: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_depth_begin(_ptr(x), _ptr(first), _ptr(x_cast),
+                                        dtype_code(x_cast.dtype) if x_cast is not None else PS_F32, _ptr(y), x.numel(),
+                                        _stream()), "depth_begin")
+
+    # ------------------------------------------------------------------ minGRU
+    def mingru_scan(self, zug, width, state, ctx, out):
+        """The gated recurrence of every entry of the step from and into the slots' state (csrc/mingru.cu).  ``zug``
+        float32 [T, 3 * width]: the update gate's, the candidate's and the output gate's projections side by side;
+        ``state`` float32 [slots, width]; ``out`` [T, width] in the compute type."""
+        _require(zug, "zug", torch.float32)
+        _require(state, "state", torch.float32)
+        _require(out, "out", self.dtype)
+        T = zug.shape[0]
+        if (zug.shape[1] != 3 * width or out.shape != (T, width) or state.shape[1] != width or zug.stride(1) != 1
+                or out.stride(1) != 1 or state.stride(1) != 1):
+            raise KernelError("mingru_scan: shapes do not match")
+        # long entries are cut into runs of tokens that are folded side by side (a rule of the step's shape)
+        longest = max(1, int(ctx.max_q_len))
+        segments = 1
+        while segments < 32 and segments * 16 < longest:
+            segments *= 2
+        self.launches += 1
+        _check(self.core.ps_mingru_scan(_ptr(zug), zug.stride(0), width, _ptr(state), state.stride(0), _ptr(ctx.q_start),
+                                        _ptr(ctx.item_slot), ctx.num_items, _ptr(out), out.stride(0), segments,
+                                        self.code, _stream()), "mingru_scan")
+        return out
+
+    # ------------------------------------------------------------------ short convolution over time
+    def short_conv(self, u, weight, taps, conv_channels, state, ctx, out, blend=None):
+        """out[t, c] = sum_j weight[c, j] * u[t - taps + 1 + j, c] for the first ``conv_channels`` channels, the rest
+        passed through; what lies before an entry's first token comes from ``state`` (float32
+        [slots, (taps - 1) * conv_channels]: a request's last projected rows), which is then brought up to date
+        (csrc/short_conv.cu).  ``u`` float32 [T, channels], ``out`` the same shape in the compute type.
+        ``blend`` = (mode, first channel, heads, head slot, head values, shared float32 [T, heads * head values],
+        mix float32 scalar): mode "store" leaves the convolved values of those heads in ``shared``, "mix" blends
+        them, v <- (1 - mix) v + mix * shared."""
+        _require(u, "u", torch.float32)
+        _require(out, "out", self.dtype)
+        T, channels = u.shape
+        if out.shape != u.shape or u.stride(1) != 1 or out.stride(1) != 1 or not (0 <= conv_channels <= channels):
+            raise KernelError("short_conv: shapes do not match")
+        if conv_channels:
+            _require(weight, "weight", torch.float32)
+            if weight.shape != (conv_channels, taps) or not weight.is_contiguous():
+                raise KernelError("short_conv: one row of taps per convolved channel")
+        if taps > 1 and conv_channels:
+            _require(state, "state", torch.float32)
+            if state.shape[1] != (taps - 1) * conv_channels or state.stride(1) != 1:
+                raise KernelError("short_conv: the state holds taps - 1 rows of the convolved channels")
+        else:
+            state = None
+        mode, lo, heads, slot, values, shared, mix = 0, 0, 0, 1, 1, None, None
+        if blend is not None:
+            kind, lo, heads, slot, values, shared, mix = blend
+            mode = {"store": 1, "mix": 2}[kind]
+            _require(shared, "shared", torch.float32)
+            if shared.shape != (T, heads * values) or not shared.is_contiguous() or lo + heads * slot > conv_channels:
+                raise KernelError("short_conv: the shared values do not fit")
+            if mode == 2:
+                _require(mix, "mix", torch.float32)
+        self.launches += 1
+        _check(self.core.ps_short_conv(_ptr(u), u.stride(0), _ptr(weight), taps, conv_channels, channels, _ptr(state),
+                                       state.stride(0) if state is not None else 0, _ptr(ctx.token_item),
+                                       _ptr(ctx.q_start), _ptr(ctx.item_slot), _ptr(out), out.stride(0), mode, lo, heads,
+                                       slot, values, _ptr(shared), _ptr(mix) if mode == 2 else None, T, self.code,
+                                       _stream()), "short_conv")
+        if state is not None:
+            self.launches += 1
+            _check(self.core.ps_short_conv_keep(_ptr(u), u.stride(0), taps, conv_channels, _ptr(state), state.stride(0),
+                                                _ptr(ctx.q_start), _ptr(ctx.item_slot), ctx.num_items, _stream()),
+                   "short_conv_keep")
+        return out
 
     # ------------------------------------------------------------------ routed experts
     def moe_route(self, x, router, shared_gate_w, dense, chosen, chosen_w, shared_gate, top, groups, keep, norm=None,
-                  score="softmax", normalize=True):
+                  score="softmax", normalize=True, correction=None):
         """The router of a layer of experts (csrc/moe.cu): softmax of ``x @ router.T`` in float32, the ``top``
         largest among the experts of the ``keep`` best of ``groups`` groups (0 or 1 groups: all experts stand),
         weights normalised to sum 1.  ``dense`` float32 [T, E] gets the weights (0 where not chosen), ``chosen``
@@ -1068,7 +1210,12 @@ class Ops:
         where ``shared_gate_w`` [W] is given.  ``norm`` = (raw float32 [T, W], gain float32 [W], eps): the kernel
         first writes the RMS norm of ``raw`` into ``x`` (the rows the experts' products then read) instead of
         reading ``x``.  ``score`` "sigmoid": the scores are sigmoid(z) expert by expert instead of the softmax;
-        ``normalize`` False: the weights are the chosen scores themselves."""
+        ``normalize`` False: the weights are the chosen scores themselves.  ``correction`` float32 [E]: added to the
+        scores for the election only (the weights stay the scores)."""
+        if correction is not None:
+            _require(correction, "correction", torch.float32)
+            if correction.numel() != router.shape[0] or not correction.is_contiguous():
+                raise KernelError("moe_route: one correction per expert")
         if score not in ("softmax", "sigmoid"):
             raise KernelError(f"moe_route: unknown score {score!r}")
         T, W = x.shape
@@ -1100,8 +1247,8 @@ class Ops:
                                       _ptr(dense), _ptr(chosen), _ptr(chosen_w), _ptr(shared_gate), T, W, E, top,
                                       int(groups or 0), int(keep or 0), self.code, _ptr(raw),
                                       raw.stride(0) if raw is not None else 0, _ptr(gain), float(eps),
-                                      1 if score == "sigmoid" else 0, 1 if normalize else 0, _stream()),
-               "moe_route")
+                                      1 if score == "sigmoid" else 0, 1 if normalize else 0, _ptr(correction),
+                                      _stream()), "moe_route")
 
     @staticmethod
     def _gate_form(form):

@@ -44,13 +44,13 @@ def build_engine(model: str, seed: int = 0, **engine_options):
         return Engine.from_folder(model, config)
     if model in NAMED_CONFIGS:
         return Engine.random(named_config(model), seed, config)
-    from pagedserve_b200.config import gozunex, tefopel, zositar
+    from pagedserve_b200.config import gozunex, pagatar, tefopel, zositar
 
-    for design in (tefopel, gozunex, zositar):
+    for design in (tefopel, gozunex, zositar, pagatar):
         if model in design.NAMED_CONFIGS:
             return Engine.random(design.named_config(model), seed, config)
     known = (sorted(NAMED_CONFIGS) + sorted(tefopel.NAMED_CONFIGS) + sorted(gozunex.NAMED_CONFIGS)
-             + sorted(zositar.NAMED_CONFIGS))
+             + sorted(zositar.NAMED_CONFIGS) + sorted(pagatar.NAMED_CONFIGS))
     raise ValueError(f"--model must be a model folder or one of {known}; got {model!r}")
 
 

@@ -123,6 +123,12 @@ class Model:
         # the arrangement's carrier (the float32 rows themselves unless the blocks say otherwise)
         schedule = self.spec.schedule
         hidden = self.blocks[schedule[0].layer].begin(hidden, ctx)
+        # rows that several layers of the step touch (a mixer's ``step_shared``) outlive the layers' own tensors
+        ctx.shared = {}
+        for block in self.blocks:
+            for key, (width, dtype) in getattr(block.mixer, "step_shared", dict)().items():
+                if key not in ctx.shared:
+                    ctx.shared[key] = self.env.ops.empty((ctx.num_tokens, width), dtype, ctx.token_ids.device)
         # what a layer asks of the step arena is dead when the layer is done (the residual stream came first):
         # every layer starts from the same place in it
         arena = getattr(self.env.ops, "arena", None)

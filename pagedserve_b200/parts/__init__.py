@@ -15,4 +15,4 @@ from pagedserve_b200.parts.base import (  # noqa: F401
     part_kinds,
     register_part,
 )
-from pagedserve_b200.parts import attention, blocks, embedding, mlp, moe, norms, positions, wkv  # noqa: F401
+from pagedserve_b200.parts import attention, blocks, embedding, mingru, mlp, moe, norms, positions, wkv  # noqa: F401

@@ -111,6 +111,17 @@ class RotaryAttention(Mixer):
     query head has a learned number whose exponential is added to the softmax's denominator and to nothing else;
     values may have a size of their own (``v_dim``); residual += o W_o.  Scores, softmax, norms, angles: float32.
 
+    ``conv`` = dict(taps, suffix): directly behind the projections (biases included) every channel of q, k and v
+    passes a short causal convolution over time, y_t = sum_j w[:, j] u_(t - taps + 1 + j) with zeros before the
+    sequence's start (tensors ``<projection><suffix>`` [channels, taps]); a request keeps its last taps - 1 projected
+    rows in its slot, so a step runs only the tokens it brings.  ``rotary.scaling`` stretches the rotation
+    (:class:`RotaryPositions`).  ``value_mix`` = dict(name, role, key): a layer of role "first" leaves its values (as
+    convolved, float32) in the step's shared rows ``key``; a layer of role "later" caches v <- (1 - m) v + m * those
+    rows of the same token, m its scalar tensor ``name`` (which a "first" layer also stores and does not use).
+    ``gate_name``: the joined heads are multiplied by sigmoid(x W_g), number by number, before W_o.
+    With a convolution or a gate the stacked product leaves float32 rows, and one kernel convolves, blends the
+    values, passes the gate's columns through and rounds to the compute type.
+
     ``kv_source`` False: the layer has no key and value tensors (projections, biases, key gain); its run in the
     schedule names the cache layer of another layer, which has written that step's keys and values (after their
     norm and turning) before this one runs, and it brings only its own queries, mask and output projection.
@@ -124,7 +135,7 @@ class RotaryAttention(Mixer):
     params: hidden_size, n_heads, n_kv_heads, head_dim, v_dim (head_dim), scale, window, chunk, softcap,
     rotary (dict or None), q_name, k_name, v_name (None: values are the unturned keys), out_name, sink_name (None: no
     sinks), bias (False; tensors ``<name>.b``), head_norm (None, or dict(q_name, k_name, eps)), kv_source (True),
-    init_std, out_init_std.
+    conv (None), value_mix (None), gate_name (None), init_std, out_init_std.
     """
 
     graph_safe = True
@@ -153,22 +164,51 @@ class RotaryAttention(Mixer):
             raise ValueError("window must be positive")
         if p.get("chunk") is not None and (p["chunk"] <= 0 or p.get("window") is not None):
             raise ValueError("chunk must be positive, and excludes a window")
-        # the plain kernel turns heads as they are; norms, padded heads and borrowed keys take the other one
-        self.plain = (self.head_norm is None and self.slot_dim == self.dim == self.v_dim and self.kv_source)
+        rotary = p.get("rotary") or dict(dims=0, base=10000.0)
+        # the plain kernel turns heads as they are; norms, padded heads, borrowed keys and stretched rotations take
+        # the other one
+        self.plain = (self.head_norm is None and self.slot_dim == self.dim == self.v_dim and self.kv_source
+                      and not rotary.get("scaling"))
         if not self.plain and not self.has_v:
             raise ValueError("rotary_attention: head norms, padded heads and borrowed keys need a value projection")
         self.q_width = p["n_heads"] * self.slot_dim
         self.kv_width = p["n_kv_heads"] * self.slot_dim
-        rotary = p.get("rotary") or dict(dims=0, base=10000.0)
         from pagedserve_b200.parts.positions import RotaryPositions
 
         self.rotary = RotaryPositions(dict(dims=rotary["dims"], base=rotary["base"],
-                                           interleaved=rotary.get("interleaved", True), head_dim=p["head_dim"]),
-                                      prefix, env)
+                                           interleaved=rotary.get("interleaved", True), head_dim=p["head_dim"],
+                                           scaling=rotary.get("scaling")), prefix, env)
+        self.conv = p.get("conv")
+        self.value_mix = p.get("value_mix")
+        self.gate_name = p.get("gate_name")
+        if self.conv is not None:
+            taps = self.conv.get("taps")
+            if not (isinstance(taps, int) and 1 <= taps <= 16):
+                raise ValueError("rotary_attention: a convolution has 1 to 16 taps")
+        if (self.conv is not None or self.value_mix) and not (self.kv_source and self.has_v):
+            raise ValueError("rotary_attention: a convolution or mixed values need key and value projections")
+        if self.value_mix and self.value_mix.get("role") not in ("first", "later"):
+            raise ValueError("rotary_attention: value_mix.role is 'first' or 'later'")
+        # the channels that are convolved (q, k, v as laid out in the stacked product); a gate's columns follow
+        self.conv_channels = self.q_width + 2 * self.kv_width if self.conv is not None else 0
+        self.staged = self.conv is not None or self.value_mix is not None or self.gate_name is not None
 
     def cache_need(self):
         p = self.params
         return KVNeed(p["n_kv_heads"], self.slot_dim, p.get("window"), chunk=p.get("chunk"))
+
+    def state_need(self):
+        if self.conv is None or self.conv["taps"] < 2:
+            return None
+        from pagedserve_b200.cache.manager import StateNeed
+
+        return StateNeed(((self.conv["taps"] - 1) * self.conv_channels,), "float32")
+
+    def step_shared(self):
+        """Rows that live for the whole step and that several layers touch: key -> (numbers per token, dtype)."""
+        if self.value_mix and self.value_mix["role"] == "first":
+            return {self.value_mix["key"]: (self.params["n_kv_heads"] * self.v_dim, torch.float32)}
+        return {}
 
     def param_specs(self):
         p = self.params
@@ -182,6 +222,14 @@ class RotaryAttention(Mixer):
         specs = [(ParamSpec(self._n(name), (rows, W), "matmul"), ("normal", std)) for name, rows in names]
         if p.get("bias"):
             specs += [(ParamSpec(self._n(name + ".b"), (rows,), "vector"), ("normal", 0.3)) for name, rows in names]
+        if self.conv is not None:
+            taps = self.conv["taps"]
+            specs += [(ParamSpec(self._n(name + self.conv.get("suffix", ".conv")), (rows, taps), "vector"),
+                       ("normal", taps ** -0.5)) for name, rows in names]
+        if self.value_mix:
+            specs.append((ParamSpec(self._n(self.value_mix["name"]), (), "vector"), ("normal", 0.3)))
+        if self.gate_name:
+            specs.append((ParamSpec(self._n(self.gate_name), (H * self.v_dim, W), "matmul"), ("normal", std)))
         if self.head_norm:
             specs.append((ParamSpec(self._n(self.head_norm["q_name"]), (self.dim,), "vector"), ("ones_plus_normal", 0.1)))
             if self.kv_source:
@@ -210,12 +258,22 @@ class RotaryAttention(Mixer):
             kinds.append((p["k_name"], G, self.dim))
             if self.has_v:
                 kinds.append((p["v_name"], G, self.v_dim))
-        self.w_in = torch.cat([self._padded_rows(tensors[self._n(name)], heads, size) for name, heads, size in kinds],
-                              dim=0).contiguous()                   # [q + k (+ v), W]
+        stacked = [self._padded_rows(tensors[self._n(name)], heads, size) for name, heads, size in kinds]
+        if self.gate_name:                                          # the gate's rows ride behind, laid out like the heads
+            stacked.append(self._padded_rows(tensors[self._n(self.gate_name)], H, self.v_dim))
+        self.w_in = torch.cat(stacked, dim=0).contiguous()          # [q + k (+ v) (+ gate), W]
         self.b_in = None
         if p.get("bias"):
-            self.b_in = torch.cat([self._padded_rows(tensors[self._n(name + ".b")], heads, size)
-                                   for name, heads, size in kinds], dim=0).contiguous()
+            biases = [self._padded_rows(tensors[self._n(name + ".b")], heads, size) for name, heads, size in kinds]
+            if self.gate_name:
+                biases.append(biases[0].new_zeros(H * self.slot_dim))
+            self.b_in = torch.cat(biases, dim=0).contiguous()
+        self.conv_weight = None
+        if self.conv is not None:
+            suffix = self.conv.get("suffix", ".conv")
+            self.conv_weight = torch.cat([self._padded_rows(tensors[self._n(name + suffix)], heads, size)
+                                          for name, heads, size in kinds], dim=0).contiguous()      # [channels, taps]
+        self.mix = tensors[self._n(self.value_mix["name"])].reshape(1).contiguous() if self.value_mix else None
         w_out = tensors[self._n(p["out_name"])]
         if self.v_dim != self.slot_dim:                             # zero columns where the heads are padded
             w_out = self._padded_rows(w_out.t().contiguous(), H, self.v_dim).t().contiguous()
@@ -232,13 +290,38 @@ class RotaryAttention(Mixer):
         ops = self.env.ops
         tokens = x.shape[0]
         H, G, D = p["n_heads"], p["n_kv_heads"], self.slot_dim
-        projected = ops.empty((tokens, self.w_in.shape[0]), self.env.dtype, residual.device)
-        ops.linear(x, self.w_in, self.b_in, projected)
+        gate = None
+        if self.staged:
+            # float32 rows out of the product; one kernel convolves q, k and v over time from the request's kept
+            # rows, blends the values, passes the gate through and rounds to the compute type
+            raw = ops.empty((tokens, self.w_in.shape[0]), torch.float32, residual.device)
+            ops.linear(x, self.w_in, self.b_in, raw)
+            projected = ops.empty(raw.shape, self.env.dtype, residual.device)
+            blend = None
+            if self.value_mix:
+                shared = getattr(ctx, "shared", {}).get(self.value_mix["key"])
+                if shared is None or shared.shape[1] != G * self.v_dim:
+                    raise ValueError("rotary_attention: the layers that mix values do not have values of one size")
+                blend = ("store" if self.value_mix["role"] == "first" else "mix", self.q_width + self.kv_width, G, D,
+                         self.v_dim, shared, self.mix)
+            taps = self.conv["taps"] if self.conv is not None else 1
+            channels = self.conv_channels or (self.q_width + 2 * self.kv_width if blend else 0)
+            weight = self.conv_weight
+            if weight is None and channels:                       # values are mixed without a convolution: one tap of 1
+                if getattr(self, "_unit_tap", None) is None:
+                    self._unit_tap = torch.ones((channels, 1), dtype=torch.float32, device=residual.device)
+                weight = self._unit_tap
+            ops.short_conv(raw, weight, taps, channels, layer.state, ctx, projected, blend=blend)
+            if self.gate_name:
+                gate = projected[:, self.q_width + 2 * self.kv_width:]
+        else:
+            projected = ops.empty((tokens, self.w_in.shape[0]), self.env.dtype, residual.device)
+            ops.linear(x, self.w_in, self.b_in, projected)
         q = projected[:, :self.q_width]
         k = v = None
         if self.kv_source:
             k = projected[:, self.q_width:self.q_width + self.kv_width]
-            v = projected[:, self.q_width + self.kv_width:] if self.has_v else None
+            v = projected[:, self.q_width + self.kv_width:self.q_width + 2 * self.kv_width] if self.has_v else None
         write_cache = p.get("write_cache", True) and self.kv_source
         if self.plain:
             self.rotary.turn_and_store(q, k, v, ctx, layer, H, G, write_cache=write_cache)
@@ -247,10 +330,12 @@ class RotaryAttention(Mixer):
             ops.head_norm_rotary_cache_write(
                 q, k, v, self.q_gain, self.k_gain, float(self.head_norm["eps"]) if self.head_norm else 0.0,
                 self.rotary.inv_freq_split(), rotary["dims"], rotary.get("interleaved", True), self.dim, ctx, layer,
-                H, G, D, write_cache=write_cache)
+                H, G, D, write_cache=write_cache, amplitude=self.rotary.amplitude)
         context = ops.empty((tokens, self.q_width), self.env.dtype, residual.device)
         ops.attention(q, k, v, context, ctx, layer, H, G, D, p.get("window"), float(p["scale"]), write_cache=False,
                       softcap=p.get("softcap"), sink=self.sink, chunk=p.get("chunk"))
+        if gate is not None:
+            ops.sigmoid_gate(context, gate)
         ops.linear(context, self.w_out, None, residual, accumulate=True)
 
 
@@ -274,12 +359,18 @@ class LatentAttention(Mixer):
     applied to the first kv_rank numbers of each head's result.  Prompt portions and single tokens take the same
     path, so a position's result does not depend on how the prompt was cut.
 
-    Launches: the stacked projection (q | down | gate), ``latent_prepare`` (norm of c, turns, cache write), the
-    per-head products with W_uk^T, attention, the per-head products with W_uv, the gate, the output product.
-    Norm statistics, angles, scores and softmax are float32.
+    With ``q_rank`` the queries go through a latent of their own: c_q = x W_dq divided by its root mean square and
+    multiplied by a gain (tensors ``dq``, ``dq.norm``), q = c_q W_uq (``uq``), instead of the one matrix ``q``.
+    ``gate`` "head": W_g has one row per head and head h's result is multiplied by sigmoid(x W_g)_h ("element", the
+    default: a row per number of the joined heads).
 
-    params: hidden_size, n_heads, flat_dim, rot_dim, v_dim, kv_rank, scale, window, eps,
-    rotary (dims, base), init_std, out_init_std; tensors q, dkv, dkv.norm, uk, uv, g, o.
+    Launches: the stacked projection (q or c_q | down | gate), with ``q_rank`` the norm of c_q and the product with
+    W_uq, ``latent_prepare`` (norm of c, turns, cache write), the per-head products with W_uk^T, attention, the
+    per-head products with W_uv, the gate, the output product.  Norm statistics, angles, scores and softmax are
+    float32.
+
+    params: hidden_size, n_heads, flat_dim, rot_dim, v_dim, kv_rank, q_rank (None), gate ("element"), scale, window,
+    eps, rotary (dims, base), init_std, out_init_std; tensors q (or dq, dq.norm, uq), dkv, dkv.norm, uk, uv, g, o.
     """
 
     graph_safe = True
@@ -298,6 +389,12 @@ class LatentAttention(Mixer):
             raise ValueError("latent_attention: rotary dims must be even and at most rot_dim")
         self.q_width = p["n_heads"] * (p["flat_dim"] + p["rot_dim"])
         self.v_width = p["n_heads"] * p["v_dim"]
+        self.q_rank = p.get("q_rank")
+        if self.q_rank is not None and not (isinstance(self.q_rank, int) and self.q_rank > 0):
+            raise ValueError("latent_attention: q_rank must be a positive integer")
+        if p.get("gate", "element") not in ("element", "head"):
+            raise ValueError("latent_attention: gate is 'element' or 'head'")
+        self.gate_width = p["n_heads"] if p.get("gate", "element") == "head" else self.v_width
         from pagedserve_b200.parts.positions import RotaryPositions
 
         self.rotary = RotaryPositions(dict(dims=rotary["dims"], base=rotary["base"], interleaved=True,
@@ -310,19 +407,31 @@ class LatentAttention(Mixer):
         p = self.params
         W, H, R = p["hidden_size"], p["n_heads"], p["kv_rank"]
         std = p.get("init_std", 0.02)
-        return [(ParamSpec(self._n("q"), (self.q_width, W), "matmul"), ("normal", std)),
+        if self.q_rank is None:
+            queries = [(ParamSpec(self._n("q"), (self.q_width, W), "matmul"), ("normal", std))]
+        else:
+            queries = [(ParamSpec(self._n("dq"), (self.q_rank, W), "matmul"), ("normal", std)),
+                       (ParamSpec(self._n("dq.norm"), (self.q_rank,), "vector"), ("ones_plus_normal", 0.1)),
+                       (ParamSpec(self._n("uq"), (self.q_width, self.q_rank), "matmul"), ("normal", self.q_rank ** -0.5))]
+        return queries + [
                 (ParamSpec(self._n("dkv"), (self.row, W), "matmul"), ("normal", std)),
                 (ParamSpec(self._n("dkv.norm"), (R,), "vector"), ("ones_plus_normal", 0.1)),
                 (ParamSpec(self._n("uk"), (H * p["flat_dim"], R), "matmul"), ("normal", R ** -0.5)),
                 (ParamSpec(self._n("uv"), (self.v_width, R), "matmul"), ("normal", R ** -0.5)),
-                (ParamSpec(self._n("g"), (self.v_width, W), "matmul"), ("normal", std)),
+                (ParamSpec(self._n("g"), (self.gate_width, W), "matmul"), ("normal", std)),
                 (ParamSpec(self._n("o"), (W, self.v_width), "matmul"), ("normal", p.get("out_init_std", std)))]
 
     def bind(self, tensors):
         p = self.params
         t = lambda name: tensors[self._n(name)]
         H, d, R = p["n_heads"], p["flat_dim"], p["kv_rank"]
-        self.w_in = torch.cat([t("q"), t("dkv"), t("g")], dim=0).contiguous()          # [q | down | gate, W]
+        first = t("q") if self.q_rank is None else t("dq")
+        self.w_in = torch.cat([first, t("dkv"), t("g")], dim=0).contiguous()            # [q or c_q | down | gate, W]
+        self.first_width = first.shape[0]
+        self.q_gain = self.w_uq = None
+        if self.q_rank is not None:
+            self.q_gain = t("dq.norm").contiguous()
+            self.w_uq = t("uq").contiguous()
         self.gain = t("dkv.norm").contiguous()
         # W_uk(h)^T stacked head by head: [H * R, d], so that head h's product maps q_flat(h) to R numbers
         self.w_uk_t = t("uk").reshape(H, d, R).transpose(1, 2).reshape(H * R, d).contiguous()
@@ -336,9 +445,14 @@ class LatentAttention(Mixer):
         tokens = x.shape[0]
         projected = ops.empty((tokens, self.w_in.shape[0]), dtype, device)
         ops.linear(x, self.w_in, None, projected)
-        q = projected[:, :self.q_width]
-        down = projected[:, self.q_width:self.q_width + self.row]
-        gate = projected[:, self.q_width + self.row:]
+        q = projected[:, :self.first_width]
+        down = projected[:, self.first_width:self.first_width + self.row]
+        gate = projected[:, self.first_width + self.row:]
+        if self.q_rank is not None:
+            latent = ops.empty((tokens, self.q_rank), dtype, device)
+            ops.group_rms_norm(q, self.q_gain, float(p["eps"]), 1, latent)
+            q = ops.empty((tokens, self.q_width), dtype, device)
+            ops.linear(latent, self.w_uq, None, q)
         queries = ops.empty((tokens, H * self.row), dtype, device)
         ops.latent_prepare(q, down, self.gain, float(p["eps"]), self.rotary.inv_freq_split(), self.rotary.params["dims"],
                            ctx, layer, queries, H, d, r, R, write_cache=p.get("write_cache", True))
@@ -351,5 +465,5 @@ class LatentAttention(Mixer):
         heads = ops.empty((tokens, self.v_width), dtype, device)
         ops.linear_grouped(context.view(tokens, H, self.row)[:, :, :R].permute(1, 0, 2), self.w_uv,
                            heads.view(tokens, H, dv).permute(1, 0, 2), max_rows=64)
-        ops.sigmoid_gate(heads, gate)
+        ops.sigmoid_gate(heads, gate, span=self.v_width // self.gate_width)
         ops.linear(heads, self.w_o, None, residual, accumulate=True)

@@ -136,3 +136,81 @@ class HyperPreNormBlock(Block):
     def end(self, carrier, ctx):
         self._open(carrier, None)
         return carrier.u
+
+
+class ResidualCarrier:
+    """What runs through the layers of a model that norms its sublayers' results: the float32 rows ``x``, the same
+    rows in the compute type (``x_cast``: what the sublayers' products read; ``x`` itself in a float32 engine), the
+    zeroed float32 rows ``y`` a sublayer adds its result into, and, where the layers end with an average over
+    depth, ``history`` [entries, T, W]: the embedded rows and every layer's result so far."""
+
+    def __init__(self, x, x_cast, y, history):
+        self.x = x
+        self.x_cast = x_cast
+        self.y = y
+        self.history = history
+
+
+@register_part("block", "post_norm")
+class PostNormBlock(Block):
+    """x <- x + norm(mixer(x)); x <- x + norm(feed_forward(x)): the sublayers read the rows themselves and the norm
+    (``post_mixer``, ``post_feed_forward``: :class:`GroupRMSNorm`) is applied to what they return.  The residual rows
+    and the sums are float32.  A layer whose feed-forward is the ``none`` part has the first half only.
+
+    ``depth`` = dict(index, name, entries): the layer ends with an average over depth.  With X_0 the embedded rows and
+    X_(i+1) this layer's result (``index`` = i), what goes on to the next layer (and, behind the last, to the
+    model's norm) is sum_(j <= i+1) w[j] X_j with w the tensor ``name`` of i + 2 numbers; ``entries`` is the number
+    of layer runs of the model plus one (the rows the history holds).
+
+    A sublayer adds its result into a zeroed row exactly as it would into the residual row of a pre-norm layer, so
+    every mixer and feed-forward works here unchanged; one kernel then norms that row, adds it, clears it, stores and
+    averages over depth where the layer ends, and leaves the new rows in the compute type for the next product."""
+
+    graph_safe = True
+
+    @property
+    def required_norms(self):
+        if getattr(self.feed_forward, "is_empty", False):
+            return ("post_mixer",)
+        return ("post_mixer", "post_feed_forward")
+
+    def param_specs(self):
+        depth = self.params.get("depth")
+        if not depth:
+            return []
+        if not (0 <= depth["index"] < depth["entries"] - 1):
+            raise ValueError("post_norm: a layer's index lies below the number of history entries")
+        return [(ParamSpec(self._n(depth["name"]), (depth["index"] + 2,), "vector"),
+                 ("share_plus_normal", depth.get("init_std", 0.2)))]
+
+    def bind(self, tensors):
+        depth = self.params.get("depth")
+        self.depth_weight = tensors[self._n(depth["name"])].contiguous() if depth else None
+
+    def begin(self, hidden, ctx):
+        ops, depth = self.env.ops, self.params.get("depth")
+        history = ops.empty((depth["entries"],) + tuple(hidden.shape), torch.float32, hidden.device) if depth else None
+        x_cast = hidden if self.env.dtype == torch.float32 else ops.empty(hidden.shape, self.env.dtype, hidden.device)
+        y = ops.empty(hidden.shape, torch.float32, hidden.device)
+        ops.depth_begin(hidden, history[0] if depth else None, None if x_cast is hidden else x_cast, y)
+        return ResidualCarrier(hidden, x_cast, y, history)
+
+    def _close(self, carrier, norm, ends_layer):
+        depth = self.params.get("depth") if ends_layer else None
+        x_cast = None if carrier.x_cast is carrier.x else carrier.x_cast
+        if depth:
+            norm.add_into(carrier.y, carrier.x, x_cast, carrier.history, depth["index"] + 2, self.depth_weight)
+        else:
+            norm.add_into(carrier.y, carrier.x, x_cast)
+
+    def forward(self, hidden, ctx, layer):
+        carrier = hidden
+        alone = getattr(self.feed_forward, "is_empty", False)
+        self.mixer.forward(carrier.x_cast, carrier.y, ctx, layer)
+        self._close(carrier, self.norms["post_mixer"], alone)
+        if not alone:
+            self.feed_forward.forward(carrier.x_cast, carrier.y, ctx)
+            self._close(carrier, self.norms["post_feed_forward"], True)
+
+    def end(self, carrier, ctx):
+        return carrier.x

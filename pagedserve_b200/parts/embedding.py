@@ -34,6 +34,34 @@ class TokenEmbedding(Embedding):
         return hidden
 
 
+@register_part("embedding", "normed_token_embedding")
+class NormedTokenEmbedding(TokenEmbedding):
+    """hidden[t] = norm(table[id_t]): the token's row, then an RMS norm in groups with a gain of its own
+    (:class:`pagedserve_b200.parts.norms.GroupRMSNorm`), float32, in place.
+    params: vocab_size, hidden_size, name, init_std, norm (dict: name, eps, groups, init_std)."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        from pagedserve_b200.parts.norms import GroupRMSNorm
+
+        norm = self.params["norm"]
+        self.norm = GroupRMSNorm(dict(width=self.params["hidden_size"], eps=norm["eps"], groups=norm.get("groups", 1),
+                                      name=norm["name"], init_std=norm.get("init_std", 0.0)), prefix, env)
+
+    def param_specs(self):
+        return super().param_specs() + self.norm.param_specs()
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.norm.bind(tensors)
+
+    def forward(self, ctx, positions):
+        hidden = super().forward(ctx, positions)
+        return self.norm.forward(hidden, out=hidden)
+
+
 @register_part("embedding", "token_pair_embedding")
 class TokenPairEmbedding(TokenEmbedding):
     """hidden[t] = scale * table[id_t] + pair[row_t]: the token table times a constant, plus a row of a second

@@ -42,6 +42,8 @@ class RoutedExperts(FeedForward):
 
     params: hidden_size, n_experts, expert_ff, top, groups, group_keep, shared_ff (None: no shared expert),
     score ("softmax"), normalize (True), expert_form (None: silu), shared_limit, shared_gate (True),
+    correction_name (None; a float32 tensor of one number per expert that is added to the scores for the election
+    only: the chosen experts' weights stay their scores),
     init_std, out_init_std; tensors ``router``, ``e<i>.gate / up / down``, ``shared.gate / up / down / sg``.
     """
 
@@ -85,6 +87,8 @@ class RoutedExperts(FeedForward):
                       (ParamSpec(self._n(name + "down"), (W, F), "matmul"), ("normal", out_std))]
         if self.has_shared_gate:
             specs.append((ParamSpec(self._n("shared.sg"), (1, W), "matmul"), ("normal", std)))
+        if p.get("correction_name"):
+            specs.append((ParamSpec(self._n(p["correction_name"]), (p["n_experts"],), "vector"), ("normal", 0.1)))
         return specs
 
     def bind(self, tensors):
@@ -95,6 +99,8 @@ class RoutedExperts(FeedForward):
                                    dim=0).contiguous()           # [2 * columns, W]: per expert its gates, then its ups
         self.w_down = torch.cat([t(name + "down") for name in names], dim=1).contiguous()      # [W, columns]
         self.w_shared_gate = t("shared.sg").reshape(-1).contiguous() if self.has_shared_gate else None
+        name = self.params.get("correction_name")
+        self.correction = t(name).contiguous() if name else None
 
     def forward(self, x, residual, ctx):
         p = self.params
@@ -116,7 +122,7 @@ class RoutedExperts(FeedForward):
         shared_gate = ops.empty((tokens,), torch.float32, device) if self.w_shared_gate is not None else None
         ops.moe_route(x, self.router, self.w_shared_gate, dense, chosen, chosen_w, shared_gate, p["top"],
                       p.get("groups") or 0, p.get("group_keep") or 0, norm=norm, score=p.get("score", "softmax"),
-                      normalize=p.get("normalize", True))
+                      normalize=p.get("normalize", True), correction=self.correction)
         F, width = p["expert_ff"], p["hidden_size"]
         if self._sorted_rows(tokens, x):
             self._forward_sorted(x, residual, dense, chosen, chosen_w, shared_gate)

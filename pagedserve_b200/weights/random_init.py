@@ -7,7 +7,8 @@ same folder feeds the loader, a plain implementation and the reference model.
 
 Every part says how each of its tensors is drawn (``init`` of its ParamSpec
 companion, see ``Model.init_plan``): ``normal(std)``, ``ones_plus_normal(std)``,
-``eye_plus_normal(std)`` (a matrix near the identity).
+``eye_plus_normal(std)`` (a matrix near the identity), ``share_plus_normal(std)`` (weights of an average: one
+over the tensor's count, plus noise).
 Values are rounded to bfloat16 before they are stored, whatever the storage
 dtype, so that a bfloat16 run and a float32 run start from the same numbers.
 """
@@ -51,6 +52,8 @@ def random_tensors(config: ModelConfig, seed: int, storage_dtype: str = "bfloat1
             noise = noise + 1.0
         elif kind == "eye_plus_normal":
             noise = noise + torch.eye(shape[0], shape[1])
+        elif kind == "share_plus_normal":
+            noise = noise + 1.0 / max(noise.numel(), 1)
         elif kind != "normal":
             raise ValueError(f"unknown init kind {kind!r}")
         stored_name = spec.checkpoint_name(param.name) if spec.checkpoint_name else param.name
