@@ -282,6 +282,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         const float s0 = exp2f(m_run[0] - b0), t0 = exp2f(ma - b0), s1 = exp2f(m_run[1] - b1), t1 = exp2f(mb - b1);
         l_run[0] = l_run[0] * s0 + la * t0;
         l_run[1] = l_run[1] * s1 + lb * t1;
+        // the merged state's maximum: a CTA that leaves a partial state stores it beside the sums
+        m_run[0] = n0;
+        m_run[1] = n1;
 #pragma unroll
         for (int dn = 0; dn < HD / 8; ++dn) {
             const int d = dn * 8 + tq * 2;

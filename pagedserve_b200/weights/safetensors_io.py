@@ -93,7 +93,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dic
         tensor = tensors[name].detach().to("cpu").contiguous()
         if tensor.dtype not in _NAMES:
             raise SafetensorsError(f"tensor {name!r}: dtype {tensor.dtype} cannot be written")
-        raw = tensor.view(torch.uint8).numpy().tobytes() if tensor.numel() else b""
+        raw = tensor.reshape(-1).view(torch.uint8).numpy().tobytes() if tensor.numel() else b""     # (a scalar has no axis to view)
         header[name] = {
             "dtype": _NAMES[tensor.dtype],
             "shape": list(tensor.shape),

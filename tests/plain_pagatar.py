@@ -278,3 +278,105 @@ def read_folder(folder, dtype=torch.float64):
             raise ValueError(f"{name}: dtype {entry['dtype']}")
         tensors[name] = value.reshape(entry["shape"]).to(dtype) if value.is_floating_point() else value.reshape(entry["shape"])
     return tensors, config
+
+
+# ------------------------------------------------------------------------------- random models for the tests
+def tensor_shapes(config):
+    """{checkpoint name: shape} of a model of ``config``."""
+    W, V = config["width"], config["vocab"]
+    shapes = {"embed": (V, W), "embed.norm": (W,), "final.norm": (W,)}
+    for index, layer in enumerate(config["layers"]):
+        p, m = "l%d." % index, layer["mixer"]
+        shapes[p + "norm1"] = (W,)
+        shapes[p + "dwa"] = (index + 2,)
+        if layer["type"] == "mingru":
+            n = m["width"]
+            shapes.update({p + "mix.z": (n, W), p + "mix.z.b": (n,), p + "mix.x": (n, W), p + "mix.x.b": (n,),
+                           p + "mix.g": (n, W), p + "mix.o": (W, n)})
+        elif layer["type"] == "latent_attention":
+            H, d, r, e, R, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            shapes.update({p + "mix.dq": (Q, W), p + "mix.dq.norm": (Q,), p + "mix.uq": (H * (d + r), Q),
+                           p + "mix.dkv": (R + r, W), p + "mix.dkv.norm": (R,), p + "mix.uk": (H * d, R),
+                           p + "mix.uv": (H * e, R), p + "mix.g": (H, W), p + "mix.o": (W, H * e)})
+        else:
+            H, G, d, e, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            for name, rows in (("q", H * d), ("k", G * d), ("v", G * e)):
+                shapes[p + "mix." + name] = (rows, W)
+                shapes[p + "mix." + name + ".b"] = (rows,)
+                shapes[p + "mix." + name + ".conv"] = (rows, taps)
+            shapes.update({p + "mix.q.norm": (d,), p + "mix.k.norm": (d,), p + "mix.g": (H * e, W),
+                           p + "mix.o": (W, H * e)})
+            if m.get("v_mix"):
+                shapes[p + "mix.vmix"] = ()
+        mlp = layer.get("mlp")
+        if mlp is None:
+            continue
+        shapes[p + "norm2"] = (W,)
+        E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+        shapes[p + "mlp.router"] = (E, W)
+        shapes[p + "mlp.correction"] = (E,)
+        for e in range(E):
+            shapes[p + "mlp.e%d.gate" % e] = (ff, W)
+            shapes[p + "mlp.e%d.up" % e] = (ff, W)
+            shapes[p + "mlp.e%d.down" % e] = (W, ff)
+    return shapes
+
+
+def random_model(config, seed):
+    """Random tensors (rounded to bfloat16, stored as such) that keep activations of order one."""
+    g = torch.Generator().manual_seed(seed)
+    tensors = {}
+    for name, shape in tensor_shapes(config).items():
+        leaf = name.split(".")[-1]
+        if name == "embed":
+            value = torch.randn(shape, generator=g)
+        elif leaf in ("norm1", "norm2", "norm"):
+            value = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        elif leaf == "dwa":
+            value = 1.0 / shape[0] + 0.2 * torch.randn(shape, generator=g)
+        elif leaf == "b":
+            value = 0.5 * torch.randn(shape, generator=g)
+        elif leaf == "conv":
+            value = torch.randn(shape, generator=g) / math.sqrt(shape[1])
+        elif leaf == "vmix":
+            value = 0.3 + 0.2 * torch.randn(shape, generator=g)
+        elif leaf == "correction":
+            value = 0.3 * torch.randn(shape, generator=g)
+        elif leaf == "router":
+            value = 2.0 * torch.randn(shape, generator=g) / math.sqrt(shape[1])
+        else:
+            value = torch.randn(shape, generator=g) / math.sqrt(shape[1])
+        tensors[name] = value.to(torch.bfloat16)
+    return tensors
+
+
+def moe_mlp(experts=4, top=2, ff=24):
+    return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
+
+
+def mingru_layer(width=48, mlp=None):
+    return {"type": "mingru", "mixer": {"width": width}, "mlp": mlp}
+
+
+def latent_layer(heads=4, dim=16, rot_dim=8, vdim=16, kv_rank=32, q_rank=40, base=10000.0, scale=0.2, mlp=None):
+    return {"type": "latent_attention", "mlp": mlp,
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+                      "scale": scale, "rot": {"base": base, "dims": rot_dim}}}
+
+
+def attention_layer(heads=4, kv_heads=2, dim=16, vdim=16, chunk=12, taps=3, rot_dims=None, base=10000.0, scale=0.25,
+                    scaling=None, v_mix=True, mlp=None):
+    rot = {"base": base, "dims": dim if rot_dims is None else rot_dims}
+    if scaling:
+        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "conv": taps, "rot": rot}
+    if chunk:
+        mixer["mask"] = {"size": chunk}
+    if v_mix:
+        mixer["v_mix"] = True
+    return {"type": "attention", "mixer": mixer, "mlp": mlp}
+
+
+def make_config(layers, width=64, vocab=97, eps=1e-5, groups=2):
+    return {"architecture": "Pagatar", "layers": layers, "norm": {"eps": eps, "groups": groups}, "vocab": vocab,
+            "width": width}
