@@ -305,7 +305,9 @@ def _run_reference(args, ref):
 # its kernels alone.  Tefopel stands beside GPT-2; Gozunex (windowed attention over a cached latent, wkv layers,
 # routed experts, several residual streams) beside Tefopel (windowed attention, wkv layers, a dense feed-forward);
 # Zositar (chunked attention with normed heads and borrowed caches, routed experts with clamped activations and a
-# gated dense feed-forward) beside a Tefopel of attention layers only.
+# gated dense feed-forward) beside a Tefopel of attention layers only; Pagatar (layers that norm their sublayers'
+# results and end with an average over depth, a gated recurrence, latent attention without a window, attention with
+# short convolutions, routed experts) beside a Gozunex of equal width, depth, heads, latent and experts.
 DESIGN_SIZES = {"w1024": "w1024", "w2048": "w2048"}      # named sizes of config/tefopel.py and config/gozunex.py
 DESIGN_CONTEXT = 2048
 
@@ -330,8 +332,19 @@ def design_arm(args):
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
 
     def configs(name):
-        from pagedserve_b200.config import gozunex, tefopel, zositar
+        from pagedserve_b200.config import gozunex, pagatar, tefopel, zositar
 
+        if args.design == "pagatar":
+            # Gozunex of equal size: same width, depth, heads, flat and turning sizes, latent, experts and vocabulary;
+            # its windows as long as the chunks, its recurrent layers where the gated recurrence stands, two residual
+            # streams (one pass over the rows per sublayer, as the norm and sums behind a sublayer are here), no shared
+            # expert
+            size = pagatar.NAMED_CONFIGS["pagatar-" + name]
+            like = gozunex.repeating_config(width=size["width"], heads=size["heads"], dim=size["head_dim"],
+                                            rot_dim=size["rot_dim"], kv_rank=size["kv_rank"], experts=size["experts"],
+                                            top=size["top"], ff=size["expert_ff"], layers=size["layers"],
+                                            wkv_heads=size["width"] // 64, window=size["chunk"], vocab=size["vocab"])
+            return size, {"pagatar": pagatar.named_config("pagatar-" + name), "gozunex": like}
         if args.design == "zositar":
             # Tefopel of equal size without wkv layers: same width, depth, heads and head size, a window as long as
             # the chunk, a dense feed-forward as wide as what one token uses of the experts
@@ -452,6 +465,36 @@ def design_arm(args):
             run = microbench.time_experts(2048, width, size["experts"], size["top"], size["ff"])
             kernels[f"experts_2048_tokens_{name}"] = {**run, "frac_tensor": run["tflops"] / tensor,
                                                       "dense_frac_tensor": run["dense_tflops"] / tensor}
+    elif args.dtype == "bfloat16" and not args.skip_points and args.design == "pagatar":
+        from pagedserve_b200.config import pagatar
+
+        hbm, tensor = peaks["hbm_gbs"], peaks["bf16_tflops"]
+        kernels = report["kernels"]
+
+        def of_hbm(run):
+            return {**run, "frac_hbm": run["gbs"] / hbm}
+
+        for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
+            size = pagatar.NAMED_CONFIGS["pagatar-" + name]
+            H, d, width, entries = size["heads"], size["head_dim"], size["width"], size["layers"] // 2 + 1
+            # the gated recurrence beside the recurrence with a matrix state per head, at equal width
+            for label, items, each in (("prefill_2x1024", 2, 1024), ("decode_b64", 64, 1), ("decode_b8", 8, 1)):
+                kernels[f"recurrence_{label}_{name}"] = {
+                    "gozunex": of_hbm(microbench.time_wkv(items, each, width // 64, 64, width)),
+                    "pagatar": of_hbm(microbench.time_mingru(items, each, width))}
+            # what closes a sublayer: the norm, the residual sum and the average over depth (a layer in the middle of
+            # the model) beside the update of two residual streams
+            for label, tokens in (("prefill_2048", 2048), ("decode_b64", 64)):
+                kernels[f"sublayer_close_{label}_{name}"] = {
+                    "gozunex": of_hbm(microbench.time_hyper_step(tokens, width, 2)),
+                    "pagatar": of_hbm(microbench.time_post_norm_add(tokens, width, 2, entries))}
+                # what stands between the projections and attention: the convolution over q | k | v beside the kernel
+                # that turns queries and keys and fills the pages
+                like = microbench.time_cache_write(tokens, H, H, d, rot_dims=(d // 4) * 2)
+                kernels[f"after_projection_{label}_{name}"] = {
+                    "tefopel": {"us": like["us"], "gbs": like["gbs"], "frac_hbm": like["gbs"] / hbm},
+                    "pagatar_convolution": of_hbm(microbench.time_short_conv(tokens, 2 if tokens > 64 else tokens, H, H, d, 3)),
+                    "pagatar_norm_turn_write": of_hbm(microbench.time_head_norm_cache_write(tokens, H, H, d, rot_dims=d))}
     elif args.dtype == "bfloat16" and not args.skip_points and args.design == "zositar":
         from pagedserve_b200.config import zositar
 
@@ -536,7 +579,7 @@ def main():
     parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
                         help="instead of the decode measurement: this many requests (prompts U[64,1024), outputs "
                              "U[32,256]) through the scheduler, chunked prefill under a 2,048-token budget")
-    parser.add_argument("--design", default=None, choices=("tefopel", "gozunex", "zositar"),
+    parser.add_argument("--design", default=None, choices=("tefopel", "gozunex", "zositar", "pagatar"),
                         help="instead of the default workload: prefill and decode throughput of this design at a few "
                              "sizes beside GPT-2 of equal size, and its kernels alone against the measured peaks")
     parser.add_argument("--design-sizes", default=None, help="comma-separated names out of: " + ", ".join(DESIGN_SIZES))

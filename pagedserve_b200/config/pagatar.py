@@ -240,10 +240,12 @@ def repeating_config(width: int, heads: int, head_dim: int, layers: int, chunk: 
 NAMED_CONFIGS = {
     "pagatar-tiny": dict(width=64, heads=4, head_dim=16, layers=3, chunk=24, vocab=512, experts=4, top=2, expert_ff=32,
                          kv_heads=2, kv_rank=32, q_rank=48, rot_dim=8),
-    "pagatar-w1024": dict(width=1024, heads=16, head_dim=64, layers=9, chunk=1024, vocab=32000, experts=8, top=2,
-                          expert_ff=1024, kv_rank=96, q_rank=512, rot_dim=32),
-    "pagatar-w2048": dict(width=2048, heads=16, head_dim=128, layers=9, chunk=1024, vocab=32000, experts=8, top=2,
-                          expert_ff=2048, kv_rank=96, q_rank=1024, rot_dim=32),
+    "pagatar-w1024": dict(width=1024, heads=16, head_dim=64, layers=8, chunk=1024, vocab=32000, experts=8, top=2,
+                          expert_ff=1024, kv_rank=96, q_rank=512, rot_dim=32,
+                          pattern=("latent_attention", "attention", "latent_attention", "mingru")),
+    "pagatar-w2048": dict(width=2048, heads=16, head_dim=128, layers=8, chunk=1024, vocab=32000, experts=8, top=2,
+                          expert_ff=2048, kv_rank=96, q_rank=1024, rot_dim=32,
+                          pattern=("latent_attention", "attention", "latent_attention", "mingru")),
 }
 
 

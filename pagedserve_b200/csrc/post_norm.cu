@@ -53,36 +53,80 @@ group_rms_norm_kernel(const TIn* x, long long x_stride, const int* __restrict__ 
     for (int j = threadIdx.x; j < H; j += blockDim.x) target[j] = from_float<TOut>(staged[j] * inverse[j / run] * gain[j]);
 }
 
-template <typename TC>
+// V numbers per access (4 where the width allows it).  The older entries of the history do not depend on the
+// sublayer's row: their weighted sum and the residual row are fetched in the first pass, beside the row itself, so
+// that their latency lies behind the row's statistics instead of behind them.
+template <int V> struct PackOf;
+template <> struct PackOf<1> { float v[1]; };
+template <> struct __align__(16) PackOf<4> { float v[4]; };
+
+template <int V> __device__ __forceinline__ void store_cast(float* p, const PackOf<V>& a) { *reinterpret_cast<PackOf<V>*>(p) = a; }
+template <int V> __device__ __forceinline__ void store_cast(__nv_bfloat16* p, const PackOf<V>& a) {
+    if constexpr (V == 4) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a.v[0], a.v[1]), hi = __floats2bfloat162_rn(a.v[2], a.v[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = packed;
+    } else {
+        p[0] = __float2bfloat16_rn(a.v[0]);
+    }
+}
+
+template <typename TC, int V>
 __global__ void __launch_bounds__(GROUP_NORM_THREADS)
 post_norm_add_kernel(float* __restrict__ y, float* __restrict__ x, int H, int groups, const float* __restrict__ gain,
-                     float eps, TC* __restrict__ x_cast, float* __restrict__ history, long long history_stride,
+                     float eps, TC* __restrict__ x_cast, float* history, long long history_stride,
                      int n_history, const float* __restrict__ weight) {
-    extern __shared__ float staged[];
+    using Pack = PackOf<V>;
+    extern __shared__ __align__(16) float staged[];          // the sublayer's row, the residual row, the older entries' sum
     __shared__ float inverse[GROUP_NORM_MAX_GROUPS];
+    float* row = staged;
+    float* kept = staged + H;
+    float* older = staged + 2 * H;
     pdl_prologue();
     y = pdl_fresh(y);
     x = pdl_fresh(x);
     history = pdl_fresh(history);
     const size_t base = (size_t)blockIdx.x * H;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        staged[j] = y[base + j];
-        y[base + j] = 0.f;
+    for (int j = V * threadIdx.x; j < H; j += V * blockDim.x) {
+        const Pack a = *reinterpret_cast<const Pack*>(y + base + j);
+        const Pack b = *reinterpret_cast<const Pack*>(x + base + j);
+        Pack sum;
+#pragma unroll
+        for (int i = 0; i < V; ++i) sum.v[i] = 0.f;
+        if (history) {
+            for (int d = 0; d < n_history - 1; ++d) {
+                const Pack h = *reinterpret_cast<const Pack*>(history + (size_t)d * history_stride + base + j);
+                const float w = weight[d];
+#pragma unroll
+                for (int i = 0; i < V; ++i) sum.v[i] = fmaf(w, h.v[i], sum.v[i]);
+            }
+        }
+        Pack zero;
+#pragma unroll
+        for (int i = 0; i < V; ++i) zero.v[i] = 0.f;
+        *reinterpret_cast<Pack*>(y + base + j) = zero;
+        *reinterpret_cast<Pack*>(row + j) = a;
+        *reinterpret_cast<Pack*>(kept + j) = b;
+        *reinterpret_cast<Pack*>(older + j) = sum;
     }
     __syncthreads();
-    group_inverse_rms(staged, H, groups, eps, inverse);
+    group_inverse_rms(row, H, groups, eps, inverse);
     __syncthreads();
     const int run = H / groups;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        float v = x[base + j] + staged[j] * inverse[j / run] * gain[j];
-        if (history) {
-            history[(size_t)(n_history - 1) * history_stride + base + j] = v;
-            float sum = 0.f;
-            for (int d = 0; d < n_history - 1; ++d) sum = fmaf(weight[d], history[(size_t)d * history_stride + base + j], sum);
-            v = fmaf(weight[n_history - 1], v, sum);
+    const float newest = history ? weight[n_history - 1] : 1.f;
+    for (int j = V * threadIdx.x; j < H; j += V * blockDim.x) {
+        const Pack g = *reinterpret_cast<const Pack*>(gain + j);
+        Pack v, out;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            v.v[i] = kept[j + i] + row[j + i] * inverse[(j + i) / run] * g.v[i];
+            out.v[i] = history ? fmaf(newest, v.v[i], older[j + i]) : v.v[i];
         }
-        x[base + j] = v;
-        if (x_cast) x_cast[base + j] = from_float<TC>(v);
+        if (history) *reinterpret_cast<Pack*>(history + (size_t)(n_history - 1) * history_stride + base + j) = v;
+        *reinterpret_cast<Pack*>(x + base + j) = out;
+        if (x_cast) store_cast<V>(x_cast + base + j, out);
     }
 }
 
@@ -136,16 +180,29 @@ PS_EXPORT int ps_post_norm_add(float* y, float* x, int T, int H, int groups, con
     if (T <= 0) return PS_OK;
     if (!y || !x || !gain || H <= 0 || groups <= 0 || H % groups) return PS_ERR_BAD_ARGUMENT;
     if (history && (!weight || n_history < 1)) return PS_ERR_BAD_ARGUMENT;
-    if (groups > ps::GROUP_NORM_MAX_GROUPS || (size_t)H * sizeof(float) > 48 * 1024) return PS_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)3 * H * sizeof(float);
+    if (groups > ps::GROUP_NORM_MAX_GROUPS || smem > 200 * 1024) return PS_ERR_UNSUPPORTED;
+    if (x_cast && cast_dtype != PS_F32 && cast_dtype != PS_BF16) return PS_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)H * sizeof(float);
-    if (!x_cast || cast_dtype == PS_F32)
-        return ps::launch_pdl(ps::post_norm_add_kernel<float>, dim3(T), dim3(ps::GROUP_NORM_THREADS), smem, s, y, x, H,
-                              groups, gain, eps, (float*)x_cast, history, history_stride, n_history, weight);
-    if (cast_dtype == PS_BF16)
-        return ps::launch_pdl(ps::post_norm_add_kernel<__nv_bfloat16>, dim3(T), dim3(ps::GROUP_NORM_THREADS), smem, s, y, x,
-                              H, groups, gain, eps, (__nv_bfloat16*)x_cast, history, history_stride, n_history, weight);
-    return PS_ERR_UNSUPPORTED;
+    const bool bf16 = x_cast && cast_dtype == PS_BF16;
+    const bool by4 = H % 4 == 0 && history_stride % 4 == 0 &&
+                     !(((uintptr_t)y | (uintptr_t)x | (uintptr_t)gain | (uintptr_t)history) & 15) &&
+                     !((uintptr_t)x_cast & (bf16 ? 7 : 15));
+#define PS_POST_NORM(TYPE, V)                                                                                        \
+    do {                                                                                                             \
+        static size_t raised[ps::MAX_DEVICES] = {0};                                                                 \
+        auto kernel = ps::post_norm_add_kernel<TYPE, V>;                                                             \
+        if (!ps::ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;                       \
+        return ps::launch_pdl(kernel, dim3(T), dim3(ps::GROUP_NORM_THREADS), smem, s, y, x, H, groups, gain, eps,    \
+                              (TYPE*)x_cast, history, history_stride, n_history, weight);                            \
+    } while (0)
+    if (bf16) {
+        if (by4) PS_POST_NORM(__nv_bfloat16, 4);
+        PS_POST_NORM(__nv_bfloat16, 1);
+    }
+    if (by4) PS_POST_NORM(float, 4);
+    PS_POST_NORM(float, 1);
+#undef PS_POST_NORM
 }
 
 // x float32 [count]; first (may be null), y float32 [count]; x_cast [count] of `cast_dtype` or null.

@@ -344,6 +344,75 @@ def time_hyper_step(tokens, width, streams, iters=20):
     return {"us": seconds * 1e6, "gbs": moved / seconds / 1e9}
 
 
+def time_mingru(items, tokens_each, width, dtype=torch.bfloat16, iters=10):
+    """The gated recurrence kernel alone on ``items`` entries of ``tokens_each`` tokens; GB/s over what it must move:
+    three float32 projections in, one row out, and every entry's state in and out."""
+    from types import SimpleNamespace
+
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(dtype)
+    total = items * tokens_each
+    copies = max(1, int(200e6 // (total * width * 14)) + 1)                       # rotate past the L2
+    zug = torch.randn(copies, total, 3 * width, device="cuda")
+    state = torch.zeros(items + 1, width, device="cuda")
+    out = torch.empty(total, width, dtype=dtype, device="cuda")
+    ctx = SimpleNamespace(q_start=torch.arange(0, total + 1, tokens_each, dtype=torch.int32, device="cuda"),
+                          item_slot=torch.arange(items, dtype=torch.int32, device="cuda"), num_items=items,
+                          max_q_len=tokens_each)
+    seconds = _time(lambda i: ops.mingru_scan(zug[i % copies], width, state, ctx, out), iters, graph=True)
+    nbytes = total * width * (3 * 4 + out.element_size()) + items * width * 4 * 2
+    return {"us": seconds * 1e6, "gbs": nbytes / seconds / 1e9, "tokens_per_s": total / seconds}
+
+
+def time_post_norm_add(tokens, width, groups, entries, iters=20):
+    """The kernel that closes a sublayer of a layer that norms its sublayers' results, with the average over
+    ``entries`` rows of depth behind it; GB/s over the sublayer's row read and zeroed, the residual row read and
+    written, the new entry written, the older entries read and the rounded copy written."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    copies = max(1, int(200e6 // ((entries + 2) * tokens * width * 4)) + 1)         # rotate past the L2
+    history = torch.randn(copies, entries, tokens, width, device="cuda")
+    x = torch.randn(copies, tokens, width, device="cuda")
+    y = torch.randn(copies, tokens, width, device="cuda")
+    cast = torch.empty(tokens, width, dtype=torch.bfloat16, device="cuda")
+    gain = torch.ones(width, device="cuda")
+    weight = torch.full((entries,), 1.0 / entries, device="cuda")
+    seconds = _time(lambda i: ops.post_norm_add(y[i % copies], x[i % copies], gain, 1e-6, groups, cast,
+                                                history[i % copies], entries, weight), iters, graph=True)
+    moved = tokens * width * (4 * (4 + entries) + 2)
+    return {"us": seconds * 1e6, "gbs": moved / seconds / 1e9}
+
+
+def time_short_conv(tokens, items, heads, kv_heads, head_dim, taps, iters=20):
+    """The short convolution over q | k | v (with the gate's columns passed through and the values blended) and the
+    kernel that keeps the entries' last rows; GB/s over the float32 rows read once and the rounded rows written."""
+    from types import SimpleNamespace
+
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    conv = (heads + 2 * kv_heads) * head_dim
+    channels = conv + heads * head_dim
+    copies = max(1, int(200e6 // (tokens * channels * 6)) + 1)                     # rotate past the L2
+    u = torch.randn(copies, tokens, channels, device="cuda")
+    out = torch.empty(tokens, channels, dtype=torch.bfloat16, device="cuda")
+    weight = torch.randn(conv, taps, device="cuda")
+    state = torch.zeros(items + 1, (taps - 1) * conv, device="cuda")
+    shared = torch.randn(tokens, kv_heads * head_dim, device="cuda")
+    mix = torch.full((1,), 0.3, device="cuda")
+    each = tokens // items
+    ctx = SimpleNamespace(q_start=torch.arange(0, tokens + 1, each, dtype=torch.int32, device="cuda"),
+                          item_slot=torch.arange(items, dtype=torch.int32, device="cuda"), num_items=items,
+                          token_item=(torch.arange(tokens, device="cuda") // each).to(torch.int32))
+    blend = ("mix", (heads + kv_heads) * head_dim, kv_heads, head_dim, head_dim, shared, mix)
+    seconds = _time(lambda i: ops.short_conv(u[i % copies], weight, taps, conv, state, ctx, out, blend=blend), iters,
+                    graph=True)
+    moved = tokens * channels * 6 + tokens * kv_heads * head_dim * 4
+    return {"us": seconds * 1e6, "gbs": moved / seconds / 1e9}
+
+
 def time_experts(tokens, width, experts, top, ff, iters=10, score="softmax", normalize=True, form=None):
     """The routed part of a feed-forward of ``experts`` experts, rows sorted by expert: router, plan, gather, the
     two tcgen05 products over expert tiles, gate, combine; beside the two plain tcgen05 products of a dense

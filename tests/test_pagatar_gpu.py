@@ -758,4 +758,4 @@ def test_heads_as_rows_over_far_keys(heads, size, positions, window):
     ops.paged_attention_simt(q, want, rows, rows, pool.stride(0), row, at, table, heads, 1, size, page, window, 0.1)
     ops.shared_position_attention(q, got, rows, rows, pool.stride(0), at, table, row, heads, size, page, window, 0.1,
                                   max_kv_len=max(positions) + 1)
-    assert rel_err(got, want.float()) < 1.2e-2
+    assert rel_err(got, want.float().cpu()) < 1.2e-2
