@@ -17,6 +17,7 @@
 namespace ps {
 
 constexpr int MINGRU_MAX_THREADS = 1024;
+constexpr int MINGRU_AHEAD = 4;                 // tokens whose projections a thread has in flight
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
 
@@ -42,14 +43,24 @@ mingru_scan_kernel(const float* __restrict__ zug, long long row_stride, int widt
     if (segments > 1) {
         float a_all = 1.f, b_all = 0.f;
         if (live) {
-            for (int t = lo; t < hi; ++t) {
-                const float* row = zug + (size_t)(first + t) * row_stride;
-                const float z = sigmoid_f(row[c]);
-                const float u = row[width + c];
-                const float candidate = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-                const float a = 1.0f - z;
-                b_all = a * b_all + z * candidate;
-                a_all *= a;
+            // MINGRU_AHEAD tokens' gates are fetched before any of them is used: the loads do not depend on the fold
+            for (int t0 = lo; t0 < hi; t0 += MINGRU_AHEAD) {
+                float zs[MINGRU_AHEAD], us[MINGRU_AHEAD];
+#pragma unroll
+                for (int k = 0; k < MINGRU_AHEAD; ++k) {
+                    const float* row = zug + (size_t)(first + min(t0 + k, hi - 1)) * row_stride;
+                    zs[k] = row[c];
+                    us[k] = row[width + c];
+                }
+#pragma unroll
+                for (int k = 0; k < MINGRU_AHEAD; ++k) {
+                    if (t0 + k >= hi) break;
+                    const float z = sigmoid_f(zs[k]);
+                    const float candidate = us[k] >= 0.f ? us[k] + 0.5f : sigmoid_f(us[k]);
+                    const float a = 1.0f - z;
+                    b_all = a * b_all + z * candidate;
+                    a_all *= a;
+                }
             }
         }
         fold_a[segment * blockDim.x + threadIdx.x] = a_all;
@@ -59,14 +70,23 @@ mingru_scan_kernel(const float* __restrict__ zug, long long row_stride, int widt
             s = fold_a[before * blockDim.x + threadIdx.x] * s + fold_b[before * blockDim.x + threadIdx.x];
     }
     if (!live) return;
-    for (int t = lo; t < hi; ++t) {
-        const float* row = zug + (size_t)(first + t) * row_stride;
-        const float z = sigmoid_f(row[c]);
-        const float u = row[width + c];
-        const float g = row[2 * width + c];
-        const float candidate = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-        s = (1.0f - z) * s + z * candidate;
-        out[(size_t)(first + t) * out_stride + c] = from_float<TC>(s * (g / (1.0f + expf(-g))));
+    for (int t0 = lo; t0 < hi; t0 += MINGRU_AHEAD) {
+        float zs[MINGRU_AHEAD], us[MINGRU_AHEAD], gs[MINGRU_AHEAD];
+#pragma unroll
+        for (int k = 0; k < MINGRU_AHEAD; ++k) {
+            const float* row = zug + (size_t)(first + min(t0 + k, hi - 1)) * row_stride;
+            zs[k] = row[c];
+            us[k] = row[width + c];
+            gs[k] = row[2 * width + c];
+        }
+#pragma unroll
+        for (int k = 0; k < MINGRU_AHEAD; ++k) {
+            if (t0 + k >= hi) break;
+            const float z = sigmoid_f(zs[k]);
+            const float candidate = us[k] >= 0.f ? us[k] + 0.5f : sigmoid_f(us[k]);
+            s = (1.0f - z) * s + z * candidate;
+            out[(size_t)(first + t0 + k) * out_stride + c] = from_float<TC>(s * (gs[k] / (1.0f + expf(-gs[k]))));
+        }
     }
     if (hi == count && lo < hi) kept[c] = s;            // the segment that holds the entry's last token
 }
@@ -75,17 +95,19 @@ mingru_scan_kernel(const float* __restrict__ zug, long long row_stride, int widt
 
 // zug float32 [T, 3 * width] rows (row_stride elements apart): z', u, g' side by side; state float32
 // [slots, width] rows (state_stride apart); q_start int32 [items + 1]; item_slot int32 [items]; out [T, width] rows of
-// `dtype`.  `segments` (1 .. 32): how many runs of consecutive tokens an entry is cut into.
+// `dtype`.  `segments` (1 .. 64): how many runs of consecutive tokens an entry is cut into.
 PS_EXPORT int ps_mingru_scan(const float* zug, long long row_stride, int width, float* state, long long state_stride,
                              const int* q_start, const int* item_slot, int items, void* out, long long out_stride,
                              int segments, int dtype, void* stream) {
     if (items <= 0) return PS_OK;
     if (!zug || !state || !q_start || !item_slot || !out || width <= 0) return PS_ERR_BAD_ARGUMENT;
-    if (segments < 1 || segments > 32) return PS_ERR_BAD_ARGUMENT;
+    if (segments < 1 || segments > 64) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     int channels = ps::MINGRU_MAX_THREADS / segments;
     if (channels > 128) channels = 128;
     while (channels > 32 && channels / 2 >= width) channels /= 2;
+    // few entries of a narrow layer: fewer channels a CTA, so that the grid still covers the SMs
+    while (channels > 8 && (long long)((width + channels - 1) / channels) * items < 148) channels /= 2;
     const dim3 grid((width + channels - 1) / channels, items), block(channels, segments);
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::mingru_scan_kernel<float>, grid, block, 0, s, zug, row_stride, width, state,

@@ -1146,7 +1146,7 @@ class Ops:
         # long entries are cut into runs of tokens that are folded side by side (a rule of the step's shape)
         longest = max(1, int(ctx.max_q_len))
         segments = 1
-        while segments < 32 and segments * 16 < longest:
+        while segments < 64 and segments * 16 < longest:
             segments *= 2
         self.launches += 1
         _check(self.core.ps_mingru_scan(_ptr(zug), zug.stride(0), width, _ptr(state), state.stride(0), _ptr(ctx.q_start),
