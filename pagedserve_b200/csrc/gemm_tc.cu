@@ -585,8 +585,11 @@ int launch(const void* A, int lda, const void* W, int ldw, const float* bias, vo
         return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv,
                                               stream, ex, cg);
     }
-    // TMA can write the output when its rows start on 16-byte boundaries
+    // TMA can write the output when its rows start on 16-byte boundaries and end on one: a store is clipped at
+    // the tensor's edge in units of 16 bytes, so a row that ends inside such a unit would take the rest of the
+    // unit with it (the columns beside a view's own)
     const bool tma_out = (((uintptr_t)out & 15) == 0) && (((size_t)ldo * sizeof(TOut)) % 16 == 0) &&
+                         (((size_t)N * sizeof(TOut)) % 16 == 0) &&
                          make_out_map(&map_out, out, M, N, ldo, (int)sizeof(TOut));
     if (tma_out)
         return launch_kernel<BN, TOut, true>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex, cg);

@@ -65,6 +65,10 @@ CONFIG_D = plain.make_config(
 CONFIG_E = plain.make_config([G(40, X(4, 2, 24))], width=48, vocab=61, groups=2)
 CONFIG_F = plain.make_config([A(5, 5, 16, 16, chunk=24, taps=3, rot_dims=4, mlp=X(7, 2, 8))], width=40, vocab=77, groups=5)
 CONFIG_H = plain.make_config([L(2, 8, 4, 8, 12, 16, mlp=None)], width=32, vocab=41, groups=1)
+# latent layers whose turning part has four numbers, so that a head's flat part neither starts nor ends on a multiple
+# of eight numbers in the rows of q and in the rows attention reads: cached rows of 128 and of 192 numbers
+CONFIG_G = plain.make_config([L(4, 24, 4, 40, 124, 64, scale=0.15, mlp=None), L(6, 40, 4, 20, 188, 72, scale=0.1, mlp=None)],
+                             width=80, vocab=89, groups=2)
 # layers for keys that stand out: chunks of 12 and of 70, every earlier key hundreds of tokens back, a latent layer
 CONFIG_S = plain.make_config(
     [A(4, 2, 16, 16, chunk=12, taps=3, rot_dims=8, scale=0.25, scaling=STRETCH, v_mix=False, mlp=None),
@@ -89,6 +93,7 @@ def _middle(all_chosen):
 
 CONFIGS = {"a": (CONFIG_A, 1, 16), "b": (CONFIG_B, 2, 16), "c": (CONFIG_C, 3, 8), "d": (CONFIG_D, 4, 32),   # config, seed, page
            "e": (CONFIG_E, 5, 16), "f": (CONFIG_F, 6, 8), "h": (CONFIG_H, 7, 16), "s": (CONFIG_S, 8, 16),
+           "g": (CONFIG_G, 9, 16),
            "m": (_middle(False), 21, 16), "n": (_middle(True), 22, 16)}
 
 _FOLDERS, _TENSORS, _LOGITS, _SETTLED = {}, {}, {}, {}
@@ -240,7 +245,7 @@ def test_mixed_batches_reuse_pages_and_slots(which, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["e", "f", "h"])
+@pytest.mark.parametrize("which", ["e", "f", "h", "g"])
 def test_models_of_one_layer(which, dtype):
     sequences = sequences_for(which, [70, 3, 131, 29, 64, 1], seed=70)
     check_replay(which, dtype, helpers.trace_whole(sequences), sequences, "whole")
@@ -759,3 +764,28 @@ def test_heads_as_rows_over_far_keys(heads, size, positions, window):
     ops.shared_position_attention(q, got, rows, rows, pool.stride(0), at, table, row, heads, size, page, window, 0.1,
                                   max_kv_len=max(positions) + 1)
     assert rel_err(got, want.float().cpu()) < 1.2e-2
+
+
+@pytest.mark.parametrize("rows", [1, 40, 65, 300])
+@pytest.mark.parametrize("heads,depth,beside_in,cols,beside_out", [(8, 24, 4, 252, 4), (4, 24, 4, 124, 4), (8, 252, 4, 100, 0),
+                                                                   (2, 96, 4, 250, 6), (3, 10, 6, 20, 6), (4, 40, 8, 68, 12)])
+def test_products_of_heads_of_ragged_sizes(rows, heads, depth, beside_in, cols, beside_out):
+    """Per-head products whose inputs and results are column blocks that neither start nor end on multiples of eight
+    numbers (a latent layer with a short turning part): whatever kernels the heads are sent to, every head's result
+    is right and the columns beside it stay as they were."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    g = torch.Generator().manual_seed(rows + heads)
+    a_full = torch.randn(rows, heads * (depth + beside_in), generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(heads * cols, depth, generator=g) * depth ** -0.5).to(torch.bfloat16).to(DEV)
+    out_full = torch.full((rows, heads * (cols + beside_out)), 3.0, dtype=torch.bfloat16, device=DEV)
+    a = a_full.view(rows, heads, depth + beside_in)[:, :, :depth].permute(1, 0, 2)
+    out = out_full.view(rows, heads, cols + beside_out)[:, :, :cols].permute(1, 0, 2)
+    ops.linear_grouped(a, w, out, max_rows=64)
+    want = torch.einsum("hmk,hnk->hmn", a.float(), w.view(heads, cols, depth).float()).cpu()
+    for head in range(heads):
+        assert rel_err(out[head].float(), want[head]) < 8e-3, head
+    if beside_out:
+        assert bool((out_full.view(rows, heads, cols + beside_out)[:, :, cols:] == 3.0).all())
+    assert int(ops.status_flag(DEV).item()) == 0
