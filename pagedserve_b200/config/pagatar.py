@@ -112,8 +112,8 @@ class PagatarConfig(ModelConfig):
             mixer["rot"] = _rotation(mixer.get("rot") or {"base": 10000.0, "dims": rot_dim}, rot_dim, where, False)
             if mixer["rot"]["dims"] != rot_dim:
                 raise ConfigError(f"Pagatar: {where}: the turning part is turned whole (rot.dims = rot_dim)")
-            if mixer["kv_rank"] + rot_dim > 256:
-                raise ConfigError(f"Pagatar: {where}: kv_rank + rot_dim above 256 is not supported")
+            if mixer["kv_rank"] + rot_dim > 1024:
+                raise ConfigError(f"Pagatar: {where}: kv_rank + rot_dim above 1024 is not supported")
         else:
             for key in ("heads", "kv_heads", "dim"):
                 _positive_int(mixer.get(key), f"{where}: mixer.{key}")

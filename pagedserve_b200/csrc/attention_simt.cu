@@ -95,9 +95,11 @@ int launch_kv_append(const void* k_src, const void* v_src, int src_stride, const
 }
 
 constexpr int ATT_WARPS = 4;
-constexpr int ATT_MAX_HD = 256;
+constexpr int ATT_MAX_HD = 1024;           // NACC = 32: a lane's share of the widest head
+constexpr int ATT_USUAL_HD = 256;          // NACC = 8: the instance for every head up to here
 
-template <typename T>
+// NACC: numbers of a head's result that a lane holds (head_dim <= 32 * NACC).
+template <typename T, int NACC>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                             const T* __restrict__ k_pool, const T* __restrict__ v_pool, long long page_stride,
@@ -126,7 +128,6 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
 
     int lo = first_visible_key(p, window);
     int first_tile = lo >> 5, last_tile = p >> 5;
-    constexpr int NACC = ATT_MAX_HD / 32;
     float acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
@@ -234,16 +235,23 @@ PS_EXPORT int ps_paged_attention_simt(const void* q, int q_stride, void* out, in
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, n_heads);
     size_t smem = (size_t)(1 + ps::ATT_WARPS) * head_dim * sizeof(float);
-    if (dtype == PS_F32)
-        return ps::launch_pdl(ps::paged_attention_simt_kernel<float>, grid, dim3(ps::ATT_WARPS * 32), smem, s,
+    const bool wide = head_dim > ps::ATT_USUAL_HD;
+    if (dtype == PS_F32) {
+        auto kernel = wide ? ps::paged_attention_simt_kernel<float, ps::ATT_MAX_HD / 32>
+                           : ps::paged_attention_simt_kernel<float, ps::ATT_USUAL_HD / 32>;
+        return ps::launch_pdl(kernel, grid, dim3(ps::ATT_WARPS * 32), smem, s,
                               (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool,
                               (const float*)v_pool, page_stride, token_item, positions, block_table, bt_stride,
                               n_heads, n_kv_heads, head_dim, page_size, window, scale, softcap, sink);
-    if (dtype == PS_BF16)
-        return ps::launch_pdl(ps::paged_attention_simt_kernel<__nv_bfloat16>, grid, dim3(ps::ATT_WARPS * 32), smem, s,
+    }
+    if (dtype == PS_BF16) {
+        auto kernel = wide ? ps::paged_attention_simt_kernel<__nv_bfloat16, ps::ATT_MAX_HD / 32>
+                           : ps::paged_attention_simt_kernel<__nv_bfloat16, ps::ATT_USUAL_HD / 32>;
+        return ps::launch_pdl(kernel, grid, dim3(ps::ATT_WARPS * 32), smem, s,
                               (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                               (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride, token_item,
                               positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim, page_size, window,
                               scale, softcap, sink);
+    }
     return PS_ERR_UNSUPPORTED;
 }

@@ -805,8 +805,9 @@ class Ops:
                            layer.page_stride, n_kv_heads, head_dim, layer.page_size)
         from pagedserve_b200.kernels import tensorcore
 
-        if self.dtype == torch.float32 or head_dim % 16 != 0:
-            # the CUDA-core kernel takes every head size; the tensor-core kernels want multiples of 16
+        if self.dtype == torch.float32 or head_dim % 16 != 0 or head_dim > 256:
+            # the CUDA-core kernel takes every head size (up to 1,024); the tensor-core kernels want multiples of 16
+            # up to 256
             return self.paged_attention_simt(q, out, layer.k_pool, layer.v_pool, layer.page_stride,
                                              ctx.token_slot, ctx.positions, layer.block_table, n_heads,
                                              n_kv_heads, head_dim, layer.page_size, window, scale, softcap, sink)

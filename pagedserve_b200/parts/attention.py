@@ -380,8 +380,8 @@ class LatentAttention(Mixer):
         super().__init__(params, prefix, env)
         p = self.params
         self.row = p["kv_rank"] + p["rot_dim"]                    # the cached row, and the attention head size
-        if not (0 < self.row <= 256):
-            raise ValueError(f"latent_attention: kv_rank + rot_dim = {self.row} is not supported: at most 256")
+        if not (0 < self.row <= 1024):         # (above 256 the CUDA-core attention kernel runs in bfloat16 too)
+            raise ValueError(f"latent_attention: kv_rank + rot_dim = {self.row} is not supported: at most 1024")
         if p.get("window") is not None and p["window"] <= 0:
             raise ValueError("window must be positive")
         rotary = p.get("rotary") or dict(dims=0, base=10000.0)

@@ -39,7 +39,7 @@ def test_config_round_trip_and_registry():
     lambda c: c["layers"][0].update(type="recurrent"), lambda c: c["layers"][0].pop("mixer"),
     lambda c: c["layers"][0]["mixer"].update(width=0),
     lambda c: c["layers"][1]["mixer"].pop("q_rank"), lambda c: c["layers"][1]["mixer"].update(rot_dim=7),
-    lambda c: c["layers"][1]["mixer"]["rot"].update(dims=4), lambda c: c["layers"][1]["mixer"].update(kv_rank=250),
+    lambda c: c["layers"][1]["mixer"]["rot"].update(dims=4), lambda c: c["layers"][1]["mixer"].update(kv_rank=1020),
     lambda c: c["layers"][2]["mixer"].pop("scale"), lambda c: c["layers"][2]["mixer"].update(heads=3),
     lambda c: c["layers"][2]["mixer"]["rot"].update(dims=7), lambda c: c["layers"][2]["mixer"]["rot"].update(dims=18),
     lambda c: c["layers"][2]["mixer"]["rot"]["scaling"].pop("fast"), lambda c: c["layers"][2]["mixer"].update(conv=0),

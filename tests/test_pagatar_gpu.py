@@ -66,8 +66,10 @@ CONFIG_E = plain.make_config([G(40, X(4, 2, 24))], width=48, vocab=61, groups=2)
 CONFIG_F = plain.make_config([A(5, 5, 16, 16, chunk=24, taps=3, rot_dims=4, mlp=X(7, 2, 8))], width=40, vocab=77, groups=5)
 CONFIG_H = plain.make_config([L(2, 8, 4, 8, 12, 16, mlp=None)], width=32, vocab=41, groups=1)
 # latent layers whose turning part has four numbers, so that a head's flat part neither starts nor ends on a multiple
-# of eight numbers in the rows of q and in the rows attention reads: cached rows of 128 and of 192 numbers
-CONFIG_G = plain.make_config([L(4, 24, 4, 40, 124, 64, scale=0.15, mlp=None), L(6, 40, 4, 20, 188, 72, scale=0.1, mlp=None)],
+# of eight numbers in the rows of q and in the rows attention reads: cached rows of 128 and of 192 numbers; and a
+# cached row of more than 256 numbers (wider than the tensor-core attention kernels take)
+CONFIG_G = plain.make_config([L(4, 24, 4, 40, 124, 64, scale=0.15, mlp=None), L(6, 40, 4, 20, 188, 72, scale=0.1, mlp=None),
+                              L(3, 16, 8, 24, 300, 40, scale=0.2, mlp=None)],
                              width=80, vocab=89, groups=2)
 # layers for keys that stand out: chunks of 12 and of 70, every earlier key hundreds of tokens back, a latent layer
 CONFIG_S = plain.make_config(
