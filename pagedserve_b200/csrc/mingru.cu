@@ -40,6 +40,18 @@ mingru_scan_kernel(const float* __restrict__ zug, long long row_stride, int widt
     pdl_prologue();
     zug = pdl_fresh(zug);
     float s = live ? kept[c] : 0.f;                    // every thread reads the stored S before anyone replaces it
+    if (count == 1 && segments == 1) {                 // a decode step's entry: one token, straight through
+        if (!live) return;
+        const float* row = zug + (size_t)first * row_stride;
+        const float z = sigmoid_f(row[c]);
+        const float u = row[width + c];
+        const float g = row[2 * width + c];
+        const float candidate = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+        s = (1.0f - z) * s + z * candidate;
+        out[(size_t)first * out_stride + c] = from_float<TC>(s * (g / (1.0f + expf(-g))));
+        kept[c] = s;
+        return;
+    }
     if (segments > 1) {
         float a_all = 1.f, b_all = 0.f;
         if (live) {
