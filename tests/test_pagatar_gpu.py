@@ -791,3 +791,24 @@ def test_products_of_heads_of_ragged_sizes(rows, heads, depth, beside_in, cols, 
     if beside_out:
         assert bool((out_full.view(rows, heads, cols + beside_out)[:, :, cols:] == 3.0).all())
     assert int(ops.status_flag(DEV).item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,heads,size,beside,per_head", [(1, 4, 16, 0, True), (70, 3, 10, 6, True), (300, 8, 64, 32, True),
+                                                             (300, 8, 64, 32, False), (33, 5, 12, 4, False), (64, 2, 40, 0, False)])
+def test_the_gate_on_heads(rows, heads, size, beside, per_head, dtype):
+    """The sigmoid gate on the joined heads, one gate per head or per number, on row views with something beside them
+    (by pieces of 16 bytes where the sizes allow it, number by number else) against float64; the neighbours stay."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(dtype)
+    g = torch.Generator().manual_seed(rows + size)
+    width = heads * size
+    full = torch.randn(rows, width + beside, generator=g).to(dtype).to(DEV)
+    gates_full = (2.0 * torch.randn(rows, (heads if per_head else width) + beside, generator=g)).to(dtype).to(DEV)
+    values, gates = full[:, :width], gates_full[:, beside:]
+    want = values.double().view(rows, heads, size) * torch.sigmoid(gates.double()).view(rows, heads, -1)
+    kept = full[:, width:].clone()
+    ops.sigmoid_gate(values, gates, span=size if per_head else 1)
+    assert rel_err(values, want.view(rows, width).cpu()) < (1e-6 if dtype == torch.float32 else 5e-3)
+    assert torch.equal(full[:, width:], kept)
