@@ -115,6 +115,7 @@ class PagatarConfig(ModelConfig):
             if mixer["kv_rank"] + rot_dim > 1024:
                 raise ConfigError(f"Pagatar: {where}: kv_rank + rot_dim above 1024 is not supported")
         else:
+            mixer.setdefault("kv_heads", mixer.get("heads"))          # absent: every query head has its own
             for key in ("heads", "kv_heads", "dim"):
                 _positive_int(mixer.get(key), f"{where}: mixer.{key}")
             mixer["vdim"] = _positive_int(mixer.get("vdim", mixer["dim"]), f"{where}: mixer.vdim")
@@ -123,9 +124,13 @@ class PagatarConfig(ModelConfig):
             if max(mixer["dim"], mixer["vdim"]) > 256:
                 raise ConfigError(f"Pagatar: {where}: head sizes above 256 are not supported")
             mixer["scale"] = _number(mixer.get("scale"), f"{where}: mixer.scale")
-            mixer["conv"] = _positive_int(mixer.get("conv", 1), f"{where}: mixer.conv")
-            if mixer["conv"] > 16:
-                raise ConfigError(f"Pagatar: {where}: more than 16 taps are not supported")
+            # absent: no convolution and no '.conv' tensors (one tap is a convolution: a factor per channel)
+            if mixer.get("conv") is not None:
+                mixer["conv"] = _positive_int(mixer["conv"], f"{where}: mixer.conv")
+                if mixer["conv"] > 16:
+                    raise ConfigError(f"Pagatar: {where}: more than 16 taps are not supported")
+            else:
+                mixer["conv"] = None
             mask = mixer.get("mask")
             if mask is not None:
                 if not isinstance(mask, dict):
@@ -175,7 +180,7 @@ class PagatarConfig(ModelConfig):
         layers = copy.deepcopy(self.layers)
         for layer in layers:                       # optional keys that are absent stay absent
             if layer["type"] == "attention":
-                for key in ("mask", "rot"):
+                for key in ("mask", "rot", "conv"):
                     if layer["mixer"].get(key) is None:
                         layer["mixer"].pop(key, None)
                 if not layer["mixer"]["v_mix"]:
@@ -201,13 +206,15 @@ def latent_layer(heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_
 
 
 def attention_layer(heads: int, kv_heads: int, dim: int, chunk: Optional[int], mlp: Optional[dict],
-                    vdim: Optional[int] = None, taps: int = 3, rot_dims: Optional[int] = None, base: float = 10000.0,
+                    vdim: Optional[int] = None, taps: Optional[int] = 3, rot_dims: Optional[int] = None, base: float = 10000.0,
                     scaling: Optional[dict] = None, v_mix: bool = True, scale: Optional[float] = None) -> dict:
     rot = {"base": base, "dims": dim if rot_dims is None else rot_dims}
     if scaling is not None:
         rot["scaling"] = dict(scaling)
     mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim if vdim is None else vdim,
-             "scale": dim ** -0.5 if scale is None else scale, "conv": taps, "rot": rot}
+             "scale": dim ** -0.5 if scale is None else scale, "rot": rot}
+    if taps is not None:
+        mixer["conv"] = taps
     if chunk is not None:
         mixer["mask"] = {"size": chunk}
     if v_mix:

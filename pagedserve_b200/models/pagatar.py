@@ -75,7 +75,8 @@ def build_pagatar_spec(config: PagatarConfig) -> ModelSpec:
                             scaling=rot.get("scaling")) if rot else None,
                 q_name="mix.q", k_name="mix.k", v_name="mix.v", out_name="mix.o", sink_name=None, bias=True,
                 head_norm=dict(q_name="mix.q.norm", k_name="mix.k.norm", eps=config.norm_eps),
-                conv=dict(taps=mixer["conv"], suffix=".conv"), value_mix=value_mix, gate_name="mix.g",
+                conv=dict(taps=mixer["conv"], suffix=".conv") if mixer.get("conv") else None, value_mix=value_mix,
+                gate_name="mix.g",
                 init_std=width_std, out_init_std=(mixer["heads"] * mixer["vdim"]) ** -0.5), prefix)
         norms = {"post_mixer": PartSpec("group_rms_norm", dict(norm, name="norm1"), prefix)}
         mlp = entry["mlp"]

@@ -139,10 +139,16 @@ def short_convolution(u, w):
     return sum(padded[j:j + u.shape[0]] * w[:, j] for j in range(taps))
 
 
+def projected(tensors, prefix, m, h, name):
+    """A biased projection of an attention layer, convolved over time where the layer has a convolution."""
+    t = lambda leaf: tensors[prefix + "mix." + leaf].to(h.dtype)
+    u = h @ t(name).T + t(name + ".b")
+    return short_convolution(u, t(name + ".conv")) if m.get("conv") else u
+
+
 def attention_values(tensors, prefix, m, h):
     """The values of an attention layer as projected and convolved, before any mixing: [T, G * e]."""
-    t = lambda name: tensors[prefix + "mix." + name].to(h.dtype)
-    return short_convolution(h @ t("v").T + t("v.b"), t("v.conv"))
+    return projected(tensors, prefix, m, h, "v")
 
 
 def gated_attention(tensors, prefix, m, h, positions, eps, first_values=None):
@@ -152,8 +158,8 @@ def gated_attention(tensors, prefix, m, h, positions, eps, first_values=None):
     H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
     t = lambda name: tensors[prefix + "mix." + name].to(h.dtype)
-    q = short_convolution(h @ t("q").T + t("q.b"), t("q.conv")).reshape(T, H, d)
-    k = short_convolution(h @ t("k").T + t("k.b"), t("k.conv")).reshape(T, G, d)
+    q = projected(tensors, prefix, m, h, "q").reshape(T, H, d)
+    k = projected(tensors, prefix, m, h, "k").reshape(T, G, d)
     own = attention_values(tensors, prefix, m, h)
     v = own
     if first_values is not None:
@@ -299,11 +305,12 @@ def tensor_shapes(config):
                            p + "mix.dkv": (R + r, W), p + "mix.dkv.norm": (R,), p + "mix.uk": (H * d, R),
                            p + "mix.uv": (H * e, R), p + "mix.g": (H, W), p + "mix.o": (W, H * e)})
         else:
-            H, G, d, e, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            H, G, d, e, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m.get("conv")
             for name, rows in (("q", H * d), ("k", G * d), ("v", G * e)):
                 shapes[p + "mix." + name] = (rows, W)
                 shapes[p + "mix." + name + ".b"] = (rows,)
-                shapes[p + "mix." + name + ".conv"] = (rows, taps)
+                if taps:
+                    shapes[p + "mix." + name + ".conv"] = (rows, taps)
             shapes.update({p + "mix.q.norm": (d,), p + "mix.k.norm": (d,), p + "mix.g": (H * e, W),
                            p + "mix.o": (W, H * e)})
             if m.get("v_mix"):
@@ -369,7 +376,9 @@ def attention_layer(heads=4, kv_heads=2, dim=16, vdim=16, chunk=12, taps=3, rot_
     rot = {"base": base, "dims": dim if rot_dims is None else rot_dims}
     if scaling:
         rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
-    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "conv": taps, "rot": rot}
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "rot": rot}
+    if taps:
+        mixer["conv"] = taps
     if chunk:
         mixer["mask"] = {"size": chunk}
     if v_mix:

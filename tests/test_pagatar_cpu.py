@@ -33,6 +33,20 @@ def test_config_round_trip_and_registry():
     assert config.vocabulary_size == 97 and config.norm_groups == 2
 
 
+def test_keys_that_are_absent_stay_absent():
+    """No 'conv': no convolution, no such tensors and nothing kept; no 'kv_heads': as many as query heads."""
+    values = plain.make_config([A(4, 2, 16, 24, chunk=None, taps=None, rot_dims=8, v_mix=False, mlp=None)], width=64, vocab=31)
+    values["layers"][0]["mixer"].pop("kv_heads")
+    config = PagatarConfig.from_dict(values)
+    assert config.layers[0]["mixer"]["kv_heads"] == 4 and config.layers[0]["mixer"]["conv"] is None
+    assert "conv" not in config.to_dict()["layers"][0]["mixer"]
+    spec = build_pagatar_spec(config)
+    model = Model(spec, PartEnv(ops=None, dtype=torch.float32, device="cpu"))
+    assert model.state_needs()[0] is None
+    names = {spec.checkpoint_name(param.name) for param, _ in init_plan(spec)}
+    assert not any(name.endswith(".conv") for name in names) and "l0.mix.q.b" in names and "l0.mix.g" in names
+
+
 @pytest.mark.parametrize("change", [
     lambda c: c.update(vocab=0), lambda c: c.update(width=-3), lambda c: c.pop("norm"),
     lambda c: c["norm"].update(groups=3), lambda c: c["norm"].update(groups=0),

@@ -64,6 +64,11 @@ CONFIG_D = plain.make_config(
 # one layer of each kind alone
 CONFIG_E = plain.make_config([G(40, X(4, 2, 24))], width=48, vocab=61, groups=2)
 CONFIG_F = plain.make_config([A(5, 5, 16, 16, chunk=24, taps=3, rot_dims=4, mlp=X(7, 2, 8))], width=40, vocab=77, groups=5)
+# attention layers without a convolution (no 'conv' key, no such tensors): values are still blended in two of them
+CONFIG_I = plain.make_config([A(4, 2, 16, 24, chunk=20, taps=None, rot_dims=8, mlp=None),
+                              A(2, 1, 32, 48, chunk=None, taps=None, scaling=STRETCH, mlp=X(4, 2, 16)),
+                              A(3, 1, 16, 16, chunk=9, taps=None, v_mix=False, mlp=None)],
+                             width=56, vocab=71, groups=2)
 CONFIG_H = plain.make_config([L(2, 8, 4, 8, 12, 16, mlp=None)], width=32, vocab=41, groups=1)
 # latent layers whose turning part has four numbers, so that a head's flat part neither starts nor ends on a multiple
 # of eight numbers in the rows of q and in the rows attention reads: cached rows of 128 and of 192 numbers; and a
@@ -95,7 +100,7 @@ def _middle(all_chosen):
 
 CONFIGS = {"a": (CONFIG_A, 1, 16), "b": (CONFIG_B, 2, 16), "c": (CONFIG_C, 3, 8), "d": (CONFIG_D, 4, 32),   # config, seed, page
            "e": (CONFIG_E, 5, 16), "f": (CONFIG_F, 6, 8), "h": (CONFIG_H, 7, 16), "s": (CONFIG_S, 8, 16),
-           "g": (CONFIG_G, 9, 16),
+           "g": (CONFIG_G, 9, 16), "i": (CONFIG_I, 10, 16),
            "m": (_middle(False), 21, 16), "n": (_middle(True), 22, 16)}
 
 _FOLDERS, _TENSORS, _LOGITS, _SETTLED = {}, {}, {}, {}
@@ -247,7 +252,7 @@ def test_mixed_batches_reuse_pages_and_slots(which, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["e", "f", "h", "g"])
+@pytest.mark.parametrize("which", ["e", "f", "h", "g", "i"])
 def test_models_of_one_layer(which, dtype):
     sequences = sequences_for(which, [70, 3, 131, 29, 64, 1], seed=70)
     check_replay(which, dtype, helpers.trace_whole(sequences), sequences, "whole")
